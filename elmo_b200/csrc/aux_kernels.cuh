@@ -1,0 +1,174 @@
+// Bandwidth-bound helper kernels around the GEMMs: embedding preparation, bucketing of the sparse
+// positives by label tile, e4m3 -> bf16 weight staging, and the fixed-order final reductions.
+#pragma once
+#include "numerics.cuh"
+#include "ptx.cuh"
+
+namespace xmc {
+
+// X [batch x d] (bf16 or e4m3) -> x8 [rows8 x d] e4m3, x16 [rows16 x d] bf16, xt [d x bpad] bf16.
+// Rows/columns in [batch, bpad) are written as zero.  32x32 tiles through shared memory so that
+// both the row-major and the transposed stores are coalesced.
+template <bool IN_E4M3>
+__global__ void prep_x_kernel(const void* __restrict__ x, int batch, int bpad, int d,
+                              uint8_t* __restrict__ x8, __nv_bfloat16* __restrict__ x16,
+                              __nv_bfloat16* __restrict__ xt) {
+  __shared__ float tile[32][33];
+  const int c0 = blockIdx.x * 32, b0 = blockIdx.y * 32;
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    const int b = b0 + i, c = c0 + threadIdx.x;
+    float v = 0.f;
+    if (b < batch && c < d) {
+      if (IN_E4M3) {
+        const uint8_t raw = reinterpret_cast<const uint8_t*>(x)[(size_t)b * d + c];
+        v = e4m3x2_to_float2((uint16_t)raw).x;
+      } else {
+        v = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(x)[(size_t)b * d + c]);
+      }
+    }
+    tile[i][threadIdx.x] = v;
+    if (b < bpad && c < d) {
+      if (x8 != nullptr) x8[(size_t)b * d + c] = (uint8_t)(float2_to_e4m3x2(v, 0.f) & 0xFFu);
+      if (x16 != nullptr) x16[(size_t)b * d + c] = __float2bfloat16_rn(v);
+    }
+  }
+  __syncthreads();
+  if (xt != nullptr) {
+    for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+      const int c = c0 + i, b = b0 + threadIdx.x;
+      if (c < d && b < bpad) xt[(size_t)c * bpad + b] = __float2bfloat16_rn(tile[threadIdx.x][i]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Positives (row, global label id) -> buckets per 128-label tile, in launch order of the tiles.
+// ---------------------------------------------------------------------------------------------
+struct BucketGeom {
+  long long label_offset;   // global id of the handle's row 0
+  long long total_rows;
+  long long rows_per_chunk; // rows of every bound weight chunk but the last
+  int sched;                // labels per scheduling chunk (multiple of 128)
+  int sched_per_chunk;      // cdiv(rows_per_chunk, sched)
+  int n_buckets;
+};
+
+__device__ __forceinline__ bool bucket_of(const BucketGeom& g, int row, int col, int batch, int* status,
+                                          int& bucket, int& lrow) {
+  if (row < 0 || row >= batch || col < 0) {
+    report(status, DEV_BAD_LABEL, row);
+    return false;
+  }
+  const long long r = (long long)col - g.label_offset;
+  if (r < 0 || r >= g.total_rows) return false;          // another shard's label
+  const long long wc = r / g.rows_per_chunk;
+  const int rr = (int)(r - wc * g.rows_per_chunk);
+  const int sc = rr / g.sched;
+  const int in = rr - sc * g.sched;
+  bucket = ((int)wc * g.sched_per_chunk + sc) * (g.sched / 128) + (in >> 7);
+  lrow = in & 127;
+  return true;
+}
+
+__global__ void bucket_count_kernel(const int32_t* __restrict__ labels, long long nnz, int batch,
+                                    BucketGeom g, int* __restrict__ count, int* status) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= nnz) return;
+  int bucket, lrow;
+  if (bucket_of(g, labels[2 * i], labels[2 * i + 1], batch, status, bucket, lrow))
+    atomicAdd(&count[bucket], 1);
+}
+
+// exclusive scan of count[0..n) into off[0..n], single block
+__global__ void bucket_scan_kernel(const int* __restrict__ count, int n, int* __restrict__ off) {
+  __shared__ int warp_sum[32];
+  __shared__ int carry;
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int base = 0; base < n; base += blockDim.x) {
+    const int i = base + threadIdx.x;
+    const int v = i < n ? count[i] : 0;
+    int s = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, s, o);
+      if (lane >= o) s += t;
+    }
+    if (lane == 31) warp_sum[warp] = s;
+    __syncthreads();
+    if (warp == 0) {
+      int w = lane < (int)(blockDim.x >> 5) ? warp_sum[lane] : 0;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, w, o);
+        if (lane >= o) w += t;
+      }
+      warp_sum[lane] = w;
+    }
+    __syncthreads();
+    const int before = carry + (warp > 0 ? warp_sum[warp - 1] : 0) + s - v;
+    if (i < n) off[i] = before;
+    __syncthreads();
+    if (threadIdx.x == blockDim.x - 1) carry = before + v;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) off[n] = carry;
+}
+
+__global__ void bucket_fill_kernel(const int32_t* __restrict__ labels, long long nnz, int batch,
+                                   BucketGeom g, const int* __restrict__ off, int* __restrict__ cursor,
+                                   uint32_t* __restrict__ entries) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= nnz) return;
+  int bucket, lrow;
+  const int row = labels[2 * i];
+  if (bucket_of(g, row, labels[2 * i + 1], batch, nullptr, bucket, lrow)) {
+    const int pos = atomicAdd(&cursor[bucket], 1);
+    entries[off[bucket] + pos] = (uint32_t)row | ((uint32_t)lrow << 16);
+  }
+}
+
+// e4m3 -> bf16 staging of one scheduling chunk of weights (exact); n16 = number of 16-byte groups
+__global__ void e4m3_to_bf16_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long long n16) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += stride) {
+    const uint4 raw = src[i];
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    uint32_t o[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float2 f = e4m3x2_to_float2((uint16_t)(w[k >> 1] >> (16 * (k & 1))));
+      o[k] = pack_bf16x2(f.x, f.y);
+    }
+    dst[2 * i] = make_uint4(o[0], o[1], o[2], o[3]);
+    dst[2 * i + 1] = make_uint4(o[4], o[5], o[6], o[7]);
+  }
+}
+
+// grad_X[b][c] = scale * sum_s partial[s][b][c], s ascending (fixed order)
+__global__ void reduce_gradx_kernel(const float* __restrict__ partial, int n_splits, int batch, int bpad,
+                                    int d, float scale, float* __restrict__ out32,
+                                    __nv_bfloat16* __restrict__ out16) {
+  const long long n = (long long)batch * d;
+  const long long slot = (long long)bpad * d;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    float s = 0.f;
+    for (int k = 0; k < n_splits; ++k) s += partial[k * slot + i];
+    s *= scale;
+    if (out32 != nullptr) out32[i] = s;
+    if (out16 != nullptr) out16[i] = __float2bfloat16_rn(s);
+  }
+}
+
+// loss = sum of n partials in index order, one thread (n is a few thousand at most)
+__global__ void reduce_loss_kernel(const double* __restrict__ partial, int n, double* __restrict__ out) {
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    double s = 0.0;
+    for (int i = 0; i < n; ++i) s += partial[i];
+    *out = s;
+  }
+}
+
+}  // namespace xmc

@@ -1,0 +1,80 @@
+// Element arithmetic shared by the epilogues: bf16/e4m3 conversions with the reference's
+// intermediate roundings, sigmoid / BCE terms, Philox4x32-10 and rounding of the updated weight.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <stdint.h>
+
+namespace xmc {
+
+__device__ __forceinline__ float bf16_round(float x) {
+  return __bfloat162float(__float2bfloat16_rn(x));
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float bf16_bits_to_float(uint32_t b16) { return __uint_as_float(b16 << 16); }
+
+// two e4m3 bytes (low byte first) -> two floats, exact
+__device__ __forceinline__ float2 e4m3x2_to_float2(uint16_t v) {
+  __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)v, __NV_E4M3);
+  return __half22float2(*reinterpret_cast<__half2*>(&h));
+}
+// two floats -> two e4m3 bytes (x in the low byte), round-to-nearest-even, saturating at +-448
+__device__ __forceinline__ uint16_t float2_to_e4m3x2(float x, float y) {
+  return (uint16_t)__nv_cvt_float2_to_fp8x2(make_float2(x, y), __NV_SATFINITE, __NV_E4M3);
+}
+
+// sigmoid of a bf16-valued float, rounded back to bf16 (the reference applies torch.sigmoid in
+// place on bf16 logits: chunked.py:112, chunked_fp8xmc_clf.py:107)
+__device__ __forceinline__ float sigmoid_bf16(float z) {
+  return bf16_round(__fdividef(1.0f, 1.0f + __expf(-z)));
+}
+// max(z,0) + log(1 + exp(-|z|)): the label-independent part of BCE-with-logits (chunked.py:57-72)
+__device__ __forceinline__ float bce_softplus(float z) {
+  return fmaxf(z, 0.0f) + log1pf(__expf(-fabsf(z)));
+}
+
+// ---------------------------------------------------------------------------------------------
+// Philox4x32-10 (Salmon et al. 2011).  One call serves 8 consecutive weight elements with 16
+// bits each: counter = (q_lo, q_hi, step_lo, step_hi), q = global element index / 8,
+// key = (seed_lo, seed_hi); element j takes half (j & 1) of output word (j >> 1).
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint2 k) {
+  constexpr uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t hi0 = __umulhi(M0, c.x), lo0 = M0 * c.x;
+    const uint32_t hi1 = __umulhi(M1, c.z), lo1 = M1 * c.z;
+    c = make_uint4(hi1 ^ c.y ^ k.x, lo1, hi0 ^ c.w ^ k.y, lo0);
+    k.x += W0;
+    k.y += W1;
+  }
+  return c;
+}
+
+// Exact stochastic rounding of fp32 w onto the e4m3 grid (subnormals included) with 16 random
+// bits; returns a float that lies on the grid.  |w| is clamped to 448, NaN propagates.
+// Normal range: add r16<<4 into the 20 discarded mantissa bits and truncate (the reference's bit
+// trick, fuse_kernel.py:28-36).  Below 2^-6 the grid is uniform (step 2^-9): shift the value into
+// the binade [2^-6, 2^-5), whose 3-bit step is 2^-9, round there and shift back (both exact).
+__device__ __forceinline__ float sr_e4m3(float w, uint32_t r16) {
+  if (w != w) return w;
+  float a = fminf(fabsf(w), 448.0f);
+  const bool small = a < 0.015625f;
+  float y = small ? a + 0.015625f : a;
+  uint32_t bits = (__float_as_uint(y) + (r16 << 4)) & 0xFFF00000u;
+  y = __uint_as_float(bits);
+  if (small) y -= 0.015625f;
+  y = fminf(y, 448.0f);
+  return copysignf(y, w);
+}
+// Stochastic rounding onto the bf16 grid: add 16 random bits below the kept mantissa, truncate
+// (fuse_kernel.py:10-17).  Returns the bf16 bit pattern.
+__device__ __forceinline__ uint32_t sr_bf16_bits(float w, uint32_t r16) {
+  return (__float_as_uint(w) + r16) >> 16;
+}
+
+}  // namespace xmc

@@ -1,0 +1,532 @@
+// C ABI of the chunked XMC classifier layer (see include/elmo_xmc.h): handle, workspaces, TMA
+// descriptors and the per-step launch schedule.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <vector>
+
+#include "../../include/elmo_xmc.h"
+#include "aux_kernels.cuh"
+#include "gemm_engine.cuh"
+#include "xmc_policies.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define CU_TRY(expr)                                                                         \
+  do {                                                                                       \
+    cudaError_t e_ = (expr);                                                                 \
+    if (e_ != cudaSuccess)                                                                   \
+      return fail(XMC_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e_), __FILE__, __LINE__); \
+  } while (0)
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                              CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                              CUtensorMapFloatOOBfill);
+
+int get_encode(EncodeFn* out) {
+  static EncodeFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    CU_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+    if (p == nullptr || q != cudaDriverEntryPointSuccess)
+      return fail(XMC_ERR_CUDA, "cuTensorMapEncodeTiled is not available in this driver");
+    fn = reinterpret_cast<EncodeFn>(p);
+  }
+  *out = fn;
+  return XMC_OK;
+}
+
+// 2-D row-major tensor [outer x inner], box [box_outer x box_inner], 128-byte swizzle, zero fill.
+int make_map(CUtensorMap* m, bool e4m3, const void* base, uint64_t inner, uint64_t outer,
+             uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer) {
+  EncodeFn enc;
+  if (int rc = get_encode(&enc)) return rc;
+  if (((uintptr_t)base & 15u) != 0 || (row_stride_bytes & 15u) != 0)
+    return fail(XMC_ERR_INVALID, "tensor base/stride must be 16-byte aligned (base %p, stride %llu)", base,
+                (unsigned long long)row_stride_bytes);
+  const cuuint64_t dims[2] = {inner, outer};
+  const cuuint64_t strides[1] = {row_stride_bytes};
+  const cuuint32_t box[2] = {box_inner, box_outer};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(m, e4m3 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                         const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(XMC_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d): inner %llu outer %llu stride %llu box %ux%u",
+                (int)r, (unsigned long long)inner, (unsigned long long)outer,
+                (unsigned long long)row_stride_bytes, box_inner, box_outer);
+  return XMC_OK;
+}
+// operand whose K runs along the rows' contiguous direction
+int make_map_kmajor(CUtensorMap* m, bool e4m3, const void* base, uint64_t k_elems, uint64_t rows,
+                    uint64_t row_stride_elems, uint32_t box_rows) {
+  const uint32_t es = e4m3 ? 1 : 2;
+  return make_map(m, e4m3, base, k_elems, rows, row_stride_elems * es, 128 / es, box_rows);
+}
+// bf16 operand stored [k_rows x mn] (MN contiguous): boxes of 64 k-rows x 64 elements
+int make_map_mnmajor(CUtensorMap* m, const void* base, uint64_t mn, uint64_t k_rows,
+                     uint64_t row_stride_elems) {
+  return make_map(m, false, base, mn, k_rows, row_stride_elems * 2, 64, 64);
+}
+
+template <class Policy>
+int launch_gemm(const CUtensorMap& a, const CUtensorMap& b, const typename Policy::Params& p, int n_tiles,
+                int sm_count, cudaStream_t stream) {
+  if (n_tiles <= 0) return XMC_OK;
+  auto kern = xmc::gemm_kernel<Policy>;
+  // per device and cheap; one process may drive several devices
+  CU_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, xmc::kSmemBytes));
+  const int grid = std::min(n_tiles, sm_count);
+  kern<<<grid, xmc::kNumThreads, xmc::kSmemBytes, stream>>>(a, b, p);
+  CU_TRY(cudaGetLastError());
+  return XMC_OK;
+}
+
+inline int cdiv(long long a, long long b) { return (int)((a + b - 1) / b); }
+inline long long round_up(long long a, long long b) { return (a + b - 1) / b * b; }
+
+}  // namespace
+
+struct xmc_handle {
+  xmc_config cfg{};
+  int sm_count = 0;
+  int bpad_max = 0;
+  int sched = 0;
+  std::vector<void*> w_ptrs;
+  std::vector<int64_t> w_rows;
+  int64_t total_rows = 0;
+  int64_t rows_per_chunk = 0;
+  int n_buckets = 0;
+  // workspaces
+  uint8_t* x8 = nullptr;           // [max(bpad_max,256) x d] e4m3
+  __nv_bfloat16* x16 = nullptr;    // [max(bpad_max,256) x d]
+  __nv_bfloat16* xt = nullptr;     // [max(d,256) x bpad_max]
+  __nv_bfloat16* G = nullptr;      // [sched x bpad_max]
+  __nv_bfloat16* w16 = nullptr;    // [sched x d] bf16 staging of an e4m3 chunk
+  float* partial = nullptr;
+  int64_t partial_floats = 0;
+  int* bucket_cnt = nullptr;       // [2 * n_buckets] counts then cursors
+  int* bucket_off = nullptr;       // [n_buckets + 1]
+  uint32_t* entries = nullptr;
+  int64_t ent_cap = 0;
+  double* loss_partial = nullptr;
+  int64_t loss_cap = 0;
+  int* status = nullptr;           // 4 ints
+  int64_t ws_bytes = 0;
+};
+
+namespace {
+
+int dev_alloc(xmc_handle* h, void** p, size_t bytes, bool zero) {
+  CU_TRY(cudaMalloc(p, bytes));
+  if (zero) CU_TRY(cudaMemset(*p, 0, bytes));
+  h->ws_bytes += (int64_t)bytes;
+  return XMC_OK;
+}
+
+struct DeviceGuard {
+  int prev = -1;
+  explicit DeviceGuard(int dev) {
+    cudaGetDevice(&prev);
+    if (prev != dev) cudaSetDevice(dev);
+  }
+  ~DeviceGuard() {
+    int cur = -1;
+    cudaGetDevice(&cur);
+    if (prev >= 0 && cur != prev) cudaSetDevice(prev);
+  }
+};
+
+xmc::BucketGeom geom_of(const xmc_handle* h) {
+  xmc::BucketGeom g;
+  g.label_offset = h->cfg.label_offset;
+  g.total_rows = h->total_rows;
+  g.rows_per_chunk = h->rows_per_chunk;
+  g.sched = h->sched;
+  g.sched_per_chunk = cdiv(h->rows_per_chunk, h->sched);
+  g.n_buckets = h->n_buckets;
+  return g;
+}
+
+int prep_x(xmc_handle* h, const void* x, int x_dtype, int batch, int bpad, bool need_x8, bool need_x16,
+           bool need_xt, cudaStream_t st) {
+  const int d = h->cfg.dim;
+  dim3 grid(cdiv(d, 32), cdiv(bpad, 32)), block(32, 8);
+  if (x_dtype == XMC_DT_E4M3)
+    xmc::prep_x_kernel<true><<<grid, block, 0, st>>>(x, batch, bpad, d, need_x8 ? h->x8 : nullptr,
+                                                     need_x16 ? h->x16 : nullptr, need_xt ? h->xt : nullptr);
+  else
+    xmc::prep_x_kernel<false><<<grid, block, 0, st>>>(x, batch, bpad, d, need_x8 ? h->x8 : nullptr,
+                                                      need_x16 ? h->x16 : nullptr, need_xt ? h->xt : nullptr);
+  CU_TRY(cudaGetLastError());
+  return XMC_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* xmc_last_error(void) { return g_err; }
+const char* xmc_version(void) { return "elmo_xmc sm_100a " __DATE__; }
+
+int xmc_create(const xmc_config* cfg, xmc_handle** out) {
+  if (cfg == nullptr || out == nullptr) return fail(XMC_ERR_INVALID, "null argument");
+  *out = nullptr;
+  if (cfg->dim <= 0 || cfg->dim % 16 != 0) return fail(XMC_ERR_INVALID, "dim must be a positive multiple of 16, got %d", cfg->dim);
+  if (cfg->max_batch <= 0 || cfg->max_batch > 65535) return fail(XMC_ERR_INVALID, "max_batch must be in [1, 65535], got %d", cfg->max_batch);
+  if (cfg->mode < XMC_MODE_BF16 || cfg->mode > XMC_MODE_SIMFP8) return fail(XMC_ERR_INVALID, "unknown mode %d", cfg->mode);
+  if (!(cfg->w_scale > 0.f)) return fail(XMC_ERR_INVALID, "w_scale must be positive");
+  if (cfg->sched_labels < 0 || cfg->sched_labels % 128 != 0) return fail(XMC_ERR_INVALID, "sched_labels must be a multiple of 128");
+  int ndev = 0;
+  CU_TRY(cudaGetDeviceCount(&ndev));
+  if (cfg->device < 0 || cfg->device >= ndev) return fail(XMC_ERR_INVALID, "device %d out of range (%d devices)", cfg->device, ndev);
+  DeviceGuard guard(cfg->device);
+  cudaDeviceProp prop;
+  CU_TRY(cudaGetDeviceProperties(&prop, cfg->device));
+  if (prop.major != 10) return fail(XMC_ERR_CUDA, "device %d is sm_%d%d; this library holds sm_100a code only", cfg->device, prop.major, prop.minor);
+
+  xmc_handle* h = new xmc_handle();
+  h->cfg = *cfg;
+  h->sm_count = prop.multiProcessorCount;
+  h->bpad_max = (int)round_up(cfg->max_batch, 16);
+  if (cfg->sched_labels > 0) {
+    h->sched = (int)cfg->sched_labels;
+  } else {
+    // keep one chunk of G (sched x bpad bf16) near 32 MB so it stays in L2 between its three consumers
+    long long s = (32ll << 20) / ((long long)h->bpad_max * 2);
+    s = std::max(1024ll, std::min(s, 131072ll));
+    h->sched = (int)(s / 128 * 128);
+  }
+  const int d = cfg->dim;
+  int rc = XMC_OK;
+  auto A = [&](void** p, size_t bytes, bool zero) { if (rc == XMC_OK) rc = dev_alloc(h, p, bytes, zero); };
+  const size_t xrows = (size_t)std::max(h->bpad_max, 256);
+  A((void**)&h->x8, xrows * d, true);
+  A((void**)&h->x16, xrows * d * 2, true);
+  A((void**)&h->xt, (size_t)std::max(d, 256) * h->bpad_max * 2, true);
+  A((void**)&h->G, (size_t)h->sched * h->bpad_max * 2, true);
+  if (cfg->mode != XMC_MODE_BF16) A((void**)&h->w16, (size_t)h->sched * d * 2, true);
+  h->partial_floats = std::max<int64_t>((int64_t)h->sm_count * 128 * 256, (int64_t)h->bpad_max * round_up(d, 256));
+  A((void**)&h->partial, (size_t)h->partial_floats * 4, true);
+  A((void**)&h->status, 4 * sizeof(int), true);
+  h->ent_cap = std::max<int64_t>(4096, (int64_t)cfg->max_batch * 64);
+  A((void**)&h->entries, (size_t)h->ent_cap * 4, false);
+  if (rc != XMC_OK) {
+    xmc_destroy(h);
+    return rc;
+  }
+  *out = h;
+  return XMC_OK;
+}
+
+int xmc_destroy(xmc_handle* h) {
+  if (h == nullptr) return XMC_OK;
+  DeviceGuard guard(h->cfg.device);
+  void* ptrs[] = {h->x8, h->x16, h->xt, h->G, h->w16, h->partial, h->bucket_cnt, h->bucket_off,
+                  h->entries, h->loss_partial, h->status};
+  for (void* p : ptrs)
+    if (p != nullptr) cudaFree(p);
+  delete h;
+  return XMC_OK;
+}
+
+int64_t xmc_workspace_bytes(const xmc_handle* h) { return h ? h->ws_bytes : 0; }
+
+int xmc_bind_weights(xmc_handle* h, int32_t n_chunks, void* const* ptrs, const int64_t* rows) {
+  if (h == nullptr || ptrs == nullptr || rows == nullptr || n_chunks <= 0) return fail(XMC_ERR_INVALID, "null/empty argument");
+  DeviceGuard guard(h->cfg.device);
+  int64_t total = 0;
+  for (int i = 0; i < n_chunks; ++i) {
+    if (ptrs[i] == nullptr || ((uintptr_t)ptrs[i] & 15u)) return fail(XMC_ERR_INVALID, "weight chunk %d: null or not 16-byte aligned", i);
+    if (rows[i] <= 0) return fail(XMC_ERR_INVALID, "weight chunk %d has %lld rows", i, (long long)rows[i]);
+    if (i + 1 < n_chunks && rows[i] != rows[0]) return fail(XMC_ERR_INVALID, "all weight chunks but the last must have equal rows (chunk %d: %lld vs %lld)", i, (long long)rows[i], (long long)rows[0]);
+    if (i + 1 == n_chunks && rows[i] > rows[0]) return fail(XMC_ERR_INVALID, "last weight chunk is larger than the others");
+    total += rows[i];
+  }
+  if (total > (1ll << 31) - 256) return fail(XMC_ERR_INVALID, "too many label rows per handle (%lld)", (long long)total);
+  h->w_ptrs.assign(ptrs, ptrs + n_chunks);
+  h->w_rows.assign(rows, rows + n_chunks);
+  h->total_rows = total;
+  h->rows_per_chunk = rows[0];
+  const int spc = cdiv(h->rows_per_chunk, h->sched);
+  const int nb = n_chunks * spc * (h->sched / 128);
+  if (nb != h->n_buckets) {
+    if (h->bucket_cnt) { cudaFree(h->bucket_cnt); h->ws_bytes -= (int64_t)h->n_buckets * 8; h->bucket_cnt = nullptr; }
+    if (h->bucket_off) { cudaFree(h->bucket_off); h->ws_bytes -= (int64_t)(h->n_buckets + 1) * 4; h->bucket_off = nullptr; }
+    if (h->loss_partial) { cudaFree(h->loss_partial); h->ws_bytes -= h->loss_cap * 8; h->loss_partial = nullptr; }
+    h->n_buckets = nb;
+    if (int rc = dev_alloc(h, (void**)&h->bucket_cnt, (size_t)nb * 8, true)) return rc;
+    if (int rc = dev_alloc(h, (void**)&h->bucket_off, (size_t)(nb + 1) * 4, true)) return rc;
+    h->loss_cap = (int64_t)n_chunks * spc * h->sm_count * 4;
+    if (int rc = dev_alloc(h, (void**)&h->loss_partial, (size_t)h->loss_cap * 8, true)) return rc;
+  }
+  return XMC_OK;
+}
+
+int xmc_check(xmc_handle* h, void* stream) {
+  if (h == nullptr) return fail(XMC_ERR_INVALID, "null handle");
+  DeviceGuard guard(h->cfg.device);
+  cudaStream_t st = (cudaStream_t)stream;
+  CU_TRY(cudaStreamSynchronize(st));
+  int host[4] = {0, 0, 0, 0};
+  CU_TRY(cudaMemcpy(host, h->status, sizeof(host), cudaMemcpyDeviceToHost));
+  if (host[0] != xmc::DEV_OK) {
+    CU_TRY(cudaMemset(h->status, 0, sizeof(host)));
+    if (host[0] == xmc::DEV_WAIT_TIMEOUT)
+      return fail(XMC_ERR_DEVICE_FLAG, "kernel wait timed out (block %d, site %d)", host[1], host[2]);
+    if (host[0] == xmc::DEV_BAD_LABEL)
+      return fail(XMC_ERR_DEVICE_FLAG, "label pair with batch row out of range or negative id (row %d)", host[2]);
+    return fail(XMC_ERR_DEVICE_FLAG, "device status %d (block %d, info %d)", host[0], host[1], host[2]);
+  }
+  return XMC_OK;
+}
+
+int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const int32_t* labels,
+             int64_t nnz, float lr, float wd, uint64_t seed, uint64_t step, uint32_t flags,
+             float* grad_x_f32, void* grad_x_bf16, double* loss_out, void* stream) {
+  if (h == nullptr || x == nullptr) return fail(XMC_ERR_INVALID, "null argument");
+  if (h->w_ptrs.empty()) return fail(XMC_ERR_STATE, "xmc_bind_weights has not been called");
+  if (x_dtype != XMC_DT_BF16) return fail(XMC_ERR_INVALID, "xmc_step takes bf16 embeddings");
+  if (batch <= 0 || batch > h->cfg.max_batch) return fail(XMC_ERR_INVALID, "batch %d outside [1, %d]", batch, h->cfg.max_batch);
+  if (nnz < 0 || (nnz > 0 && labels == nullptr)) return fail(XMC_ERR_INVALID, "labels missing");
+  if ((flags & XMC_STEP_COMPUTE_LOSS) && loss_out == nullptr) return fail(XMC_ERR_INVALID, "loss_out missing");
+  if (((uintptr_t)grad_x_f32 & 15u) || ((uintptr_t)grad_x_bf16 & 1u)) return fail(XMC_ERR_INVALID, "grad_x not aligned");
+  DeviceGuard guard(h->cfg.device);
+  cudaStream_t st = (cudaStream_t)stream;
+  const int d = h->cfg.dim, mode = h->cfg.mode;
+  const int bpad = (int)round_up(batch, 16);
+  const bool w8 = mode != XMC_MODE_BF16;
+  const bool fwd_fp8 = mode == XMC_MODE_FP8;
+  const bool want_loss = (flags & XMC_STEP_COMPUTE_LOSS) != 0;
+  const bool sr = (flags & XMC_STEP_STOCHASTIC) != 0;
+
+  // --- embeddings: e4m3 copy (forward), bf16 copy, bf16 transpose (update) ---
+  if (int rc = prep_x(h, x, x_dtype, batch, bpad, fwd_fp8, !fwd_fp8, true, st)) return rc;
+
+  // --- bucket the positives by label tile ---
+  if (nnz > h->ent_cap) {
+    CU_TRY(cudaStreamSynchronize(st));
+    CU_TRY(cudaFree(h->entries));
+    h->ws_bytes -= h->ent_cap * 4;
+    h->entries = nullptr;
+    h->ent_cap = nnz + nnz / 2;
+    if (int rc = dev_alloc(h, (void**)&h->entries, (size_t)h->ent_cap * 4, false)) return rc;
+  }
+  const xmc::BucketGeom geom = geom_of(h);
+  CU_TRY(cudaMemsetAsync(h->bucket_cnt, 0, (size_t)h->n_buckets * 8, st));
+  if (nnz > 0) {
+    xmc::bucket_count_kernel<<<cdiv(nnz, 256), 256, 0, st>>>(labels, nnz, batch, geom, h->bucket_cnt, h->status);
+    CU_TRY(cudaGetLastError());
+  }
+  xmc::bucket_scan_kernel<<<1, 1024, 0, st>>>(h->bucket_cnt, h->n_buckets, h->bucket_off);
+  CU_TRY(cudaGetLastError());
+  if (nnz > 0) {
+    xmc::bucket_fill_kernel<<<cdiv(nnz, 256), 256, 0, st>>>(labels, nnz, batch, geom, h->bucket_off,
+                                                            h->bucket_cnt + h->n_buckets, h->entries);
+    CU_TRY(cudaGetLastError());
+  }
+
+  // --- grad_X partial geometry ---
+  const int n_bt = cdiv(bpad, 128), n_dt = cdiv(d, 256);
+  int n_splits = std::max(1, h->sm_count / (n_bt * n_dt));
+  while (n_splits > 1 && (int64_t)n_splits * bpad * d > h->partial_floats) --n_splits;
+  if ((int64_t)n_splits * bpad * d > h->partial_floats) return fail(XMC_ERR_STATE, "grad_X workspace too small");
+
+  // --- operand maps that do not change across chunks ---
+  CUtensorMap map_x, map_xt, map_g_k, map_g_mn;
+  const size_t xrows = (size_t)std::max(h->bpad_max, 256);
+  if (fwd_fp8) {
+    if (int rc = make_map_kmajor(&map_x, true, h->x8, d, xrows, d, 256)) return rc;
+  } else {
+    if (int rc = make_map_kmajor(&map_x, false, h->x16, d, xrows, d, 256)) return rc;
+  }
+  if (int rc = make_map_kmajor(&map_xt, false, h->xt, bpad, std::max(d, 256), bpad, 256)) return rc;
+  if (int rc = make_map_kmajor(&map_g_k, false, h->G, bpad, h->sched, bpad, 128)) return rc;
+  if (int rc = make_map_mnmajor(&map_g_mn, h->G, bpad, h->sched, bpad)) return rc;
+
+  const float lr_eff = lr / h->cfg.w_scale;
+  const int tiles_per_sched = h->sched / 128;
+  int launch_idx = 0;
+  bool first = true;
+  int64_t row_base = 0;
+  for (size_t wc = 0; wc < h->w_ptrs.size(); ++wc) {
+    const int64_t rows_wc = h->w_rows[wc];
+    const int spc = cdiv(h->rows_per_chunk, h->sched);
+    for (int sc = 0; sc < spc; ++sc) {
+      const int64_t s0 = (int64_t)sc * h->sched;
+      if (s0 >= rows_wc) break;
+      const int rows_valid = (int)std::min<int64_t>(h->sched, rows_wc - s0);
+      const int n_lt = cdiv(rows_valid, 128);
+      const size_t esz = w8 ? 1 : 2;
+      uint8_t* wbase = reinterpret_cast<uint8_t*>(h->w_ptrs[wc]) + (size_t)s0 * d * esz;
+
+      // bf16 view of the chunk's weights for the bf16 contractions
+      const __nv_bfloat16* w16 = reinterpret_cast<const __nv_bfloat16*>(wbase);
+      if (w8) {
+        const long long n16 = (long long)rows_valid * d / 16;
+        const int blocks = (int)std::min<long long>((n16 + 255) / 256, (long long)h->sm_count * 8);
+        xmc::e4m3_to_bf16_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const uint4*>(wbase),
+                                                         reinterpret_cast<uint4*>(h->w16), n16);
+        CU_TRY(cudaGetLastError());
+        w16 = h->w16;
+      }
+
+      // forward + loss gradient -> G
+      CUtensorMap map_w;
+      if (fwd_fp8) {
+        if (int rc = make_map_kmajor(&map_w, true, wbase, d, rows_valid, d, 128)) return rc;
+      } else {
+        if (int rc = make_map_kmajor(&map_w, false, w16, d, rows_valid, d, 128)) return rc;
+      }
+      xmc::FwdParams fp;
+      fp.rows_valid = rows_valid;
+      fp.n_ltiles = n_lt;
+      fp.n_btiles = cdiv(bpad, 256);
+      fp.batch = batch;
+      fp.bpad = bpad;
+      fp.k_steps = cdiv((long long)d * (fwd_fp8 ? 1 : 2), 128);
+      fp.w_scale = h->cfg.w_scale;
+      fp.G = h->G;
+      fp.bucket_off = h->bucket_off;
+      fp.bucket_ent = h->entries;
+      fp.tile_base = ((int)wc * spc + sc) * tiles_per_sched;
+      fp.loss_partial = want_loss ? h->loss_partial + (size_t)launch_idx * h->sm_count * 4 : nullptr;
+      fp.status = h->status;
+      const int f_tiles = fp.n_ltiles * fp.n_btiles;
+      if (want_loss && std::min(f_tiles, h->sm_count) < h->sm_count) {
+        // slots of CTAs that are not launched must read as zero
+        CU_TRY(cudaMemsetAsync(fp.loss_partial, 0, (size_t)h->sm_count * 4 * sizeof(double), st));
+      }
+      int rc;
+      if (fwd_fp8) rc = want_loss ? launch_gemm<xmc::FwdPolicy<true, true>>(map_w, map_x, fp, f_tiles, h->sm_count, st)
+                                  : launch_gemm<xmc::FwdPolicy<true, false>>(map_w, map_x, fp, f_tiles, h->sm_count, st);
+      else rc = want_loss ? launch_gemm<xmc::FwdPolicy<false, true>>(map_w, map_x, fp, f_tiles, h->sm_count, st)
+                          : launch_gemm<xmc::FwdPolicy<false, false>>(map_w, map_x, fp, f_tiles, h->sm_count, st);
+      if (rc) return rc;
+
+      // grad_X partials: uses the pre-update weights (reference: chunked.py:116 precedes :119-127)
+      CUtensorMap map_w_mn;
+      if (int rc2 = make_map_mnmajor(&map_w_mn, w16, d, rows_valid, d)) return rc2;
+      xmc::GradXParams gp;
+      gp.bpad = bpad;
+      gp.d = d;
+      gp.n_btiles = n_bt;
+      gp.n_dtiles = n_dt;
+      gp.n_splits = n_splits;
+      gp.total_ksteps = cdiv(rows_valid, 64);
+      gp.accumulate = first ? 0 : 1;
+      gp.partial = h->partial;
+      gp.status = h->status;
+      if ((rc = launch_gemm<xmc::GradXPolicy>(map_g_mn, map_w_mn, gp, n_bt * n_dt * n_splits, h->sm_count, st))) return rc;
+
+      // fused dW + SGD update of the chunk, in place
+      xmc::UpdParams up;
+      up.rows_valid = rows_valid;
+      up.n_ltiles = n_lt;
+      up.n_dtiles = n_dt;
+      up.d = d;
+      up.k_steps = cdiv(bpad, 64);
+      up.W = wbase;
+      up.lr_eff = lr_eff;
+      up.wd = wd;
+      up.seed = seed;
+      up.step = step;
+      up.elem0 = (unsigned long long)(h->cfg.label_offset + row_base + s0) * (unsigned long long)d;
+      up.round_dw_bf16 = (flags & XMC_STEP_ROUND_DW_BF16) ? 1 : 0;
+      up.status = h->status;
+      const int u_tiles = n_lt * n_dt;
+      if (w8) rc = sr ? launch_gemm<xmc::UpdPolicy<true, true>>(map_g_k, map_xt, up, u_tiles, h->sm_count, st)
+                      : launch_gemm<xmc::UpdPolicy<true, false>>(map_g_k, map_xt, up, u_tiles, h->sm_count, st);
+      else rc = sr ? launch_gemm<xmc::UpdPolicy<false, true>>(map_g_k, map_xt, up, u_tiles, h->sm_count, st)
+                   : launch_gemm<xmc::UpdPolicy<false, false>>(map_g_k, map_xt, up, u_tiles, h->sm_count, st);
+      if (rc) return rc;
+      first = false;
+      ++launch_idx;
+    }
+    row_base += rows_wc;
+  }
+
+  if (grad_x_f32 != nullptr || grad_x_bf16 != nullptr) {
+    const long long n = (long long)batch * d;
+    const int blocks = (int)std::min<long long>((n + 255) / 256, (long long)h->sm_count * 8);
+    xmc::reduce_gradx_kernel<<<blocks, 256, 0, st>>>(h->partial, n_splits, batch, bpad, d, h->cfg.w_scale,
+                                                     grad_x_f32, reinterpret_cast<__nv_bfloat16*>(grad_x_bf16));
+    CU_TRY(cudaGetLastError());
+  }
+  if (want_loss) {
+    xmc::reduce_loss_kernel<<<1, 32, 0, st>>>(h->loss_partial, launch_idx * h->sm_count * 4, loss_out);
+    CU_TRY(cudaGetLastError());
+  }
+  return XMC_OK;
+}
+
+int xmc_forward_logits(xmc_handle*, const void*, int32_t, int32_t, void*, int64_t, int64_t, void*) {
+  return fail(XMC_ERR_STATE, "xmc_forward_logits: not built yet");
+}
+int xmc_forward_topk(xmc_handle*, const void*, int32_t, int32_t, int32_t, int64_t, float*, int32_t*, void*) {
+  return fail(XMC_ERR_STATE, "xmc_forward_topk: not built yet");
+}
+
+int xmc_test_gemm(int32_t device, int32_t layout, int32_t dtype, int32_t M, int32_t N, int32_t K,
+                  const void* A, const void* B, float* D, void* stream) {
+  if (A == nullptr || B == nullptr || D == nullptr || M <= 0 || N <= 0 || K <= 0) return fail(XMC_ERR_INVALID, "bad argument");
+  if (layout == 1 && dtype != XMC_DT_BF16) return fail(XMC_ERR_INVALID, "MN-major test takes bf16");
+  if (dtype != XMC_DT_BF16 && dtype != XMC_DT_E4M3) return fail(XMC_ERR_INVALID, "dtype");
+  DeviceGuard guard(device);
+  cudaDeviceProp prop;
+  CU_TRY(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10) return fail(XMC_ERR_CUDA, "device is not sm_100");
+  int* status = nullptr;
+  CU_TRY(cudaMalloc((void**)&status, 16));
+  CU_TRY(cudaMemset(status, 0, 16));
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool f8 = dtype == XMC_DT_E4M3;
+  CUtensorMap ma, mb;
+  xmc::PlainParams p;
+  p.M = M; p.N = N;
+  p.n_mtiles = cdiv(M, 128);
+  p.n_ntiles = cdiv(N, 256);
+  p.D = D;
+  p.status = status;
+  int rc;
+  if (layout == 0) {
+    if ((rc = make_map_kmajor(&ma, f8, A, K, M, K, 128))) { cudaFree(status); return rc; }
+    if ((rc = make_map_kmajor(&mb, f8, B, K, N, K, 256))) { cudaFree(status); return rc; }
+    p.k_steps = cdiv((long long)K * (f8 ? 1 : 2), 128);
+    rc = f8 ? launch_gemm<xmc::PlainPolicy<true, false>>(ma, mb, p, p.n_mtiles * p.n_ntiles, prop.multiProcessorCount, st)
+            : launch_gemm<xmc::PlainPolicy<false, false>>(ma, mb, p, p.n_mtiles * p.n_ntiles, prop.multiProcessorCount, st);
+  } else {
+    if ((rc = make_map_mnmajor(&ma, A, M, K, M))) { cudaFree(status); return rc; }
+    if ((rc = make_map_mnmajor(&mb, B, N, K, N))) { cudaFree(status); return rc; }
+    p.k_steps = cdiv(K, 64);
+    rc = launch_gemm<xmc::PlainPolicy<false, true>>(ma, mb, p, p.n_mtiles * p.n_ntiles, prop.multiProcessorCount, st);
+  }
+  if (rc == XMC_OK) {
+    cudaError_t e = cudaStreamSynchronize(st);
+    int host[4] = {0, 0, 0, 0};
+    if (e == cudaSuccess) e = cudaMemcpy(host, status, 16, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) rc = fail(XMC_ERR_CUDA, "test gemm: %s", cudaGetErrorString(e));
+    else if (host[0] != 0) rc = fail(XMC_ERR_DEVICE_FLAG, "test gemm: device status %d (block %d, site %d)", host[0], host[1], host[2]);
+  }
+  cudaFree(status);
+  return rc;
+}
+
+}  // extern "C"

@@ -1,0 +1,74 @@
+"""Counterpart of the reference's src/xmc_classifiers/chunked.py (XMCBCECHUNKEDLayer).
+
+Same constructor ``(cfg)``, attributes (``xfc_weight``, ``grad_input``, ``_dtype``, ``iteration``,
+``num_chunks``, ``chunk_size``) and methods (``xfc_forward``, ``xfc_forward_backward``).  The dense
+weight tensor lives in torch memory and is borrowed by the CUDA library; forward, loss gradient,
+grad_X and the SGD update run there.  Only bfloat16 weights are implemented on the GPU path (the
+reference also offers float32/float16 through plain torch ops): other dtypes raise.
+"""
+import torch
+from torch import nn
+
+from ..handle import XmcHandle
+from ._common import as_labels, cfg_get, draw_base_seed, dtype_map
+
+
+class XMCBCECHUNKEDLayer(nn.Module):
+    def __init__(self, cfg):
+        super().__init__()
+        self.cfg = cfg
+        self.device = torch.device(cfg.environment.device)
+        self._dtype = dtype_map[cfg.model.xmc.dtype]                                   # chunked.py:20-23
+        self._dtype = torch.float32 if cfg.training.precision.mode in ['purefp'] else self._dtype
+        self._dtype = dtype_map[cfg.training.precision.purelp_dtype] \
+            if cfg.training.precision.mode in ['purelp'] else self._dtype
+        if self._dtype != torch.bfloat16:
+            raise NotImplementedError(
+                f"elmo_b200 XMCBCECHUNKEDLayer implements bfloat16 weights on the GPU; got {self._dtype}")
+        self.num_labels = cfg.data.num_labels
+        self.num_chunks = cfg.model.xmc.num_chunks
+        self.chunk_size = (self.num_labels + self.num_chunks - 1) // self.num_chunks   # chunked.py:30
+        d = cfg.model.xmc.input_features
+        self.input_features = d
+        self.xfc_weight = torch.empty(self.num_labels, d, dtype=self._dtype).to(self.device)
+        nn.init.normal_(self.xfc_weight, mean=0.0, std=0.02)                           # chunked.py:34
+        self._grad_buf = torch.zeros(cfg.data.batch_size, d, dtype=self._dtype, device=self.device)
+        self.grad_input = self._grad_buf
+        self.loss = torch.tensor(0.0, device=self.device)
+        self._loss_dev = torch.zeros(1, dtype=torch.float64, device=self.device)
+        self.iteration = 0
+        # the reference's bf16 path always rounds stochastically (stochastic_rounding_kernel.py:82-89)
+        self.rounding = cfg_get(cfg, 'training.xmc.rounding', 'sr')
+        self.base_seed = draw_base_seed()
+        self._handle = XmcHandle(self.device, d, cfg.data.batch_size, 'bf16',
+                                 label_offset=cfg_get(cfg, 'model.xmc.label_offset', 0),
+                                 sched_labels=cfg_get(cfg, 'model.xmc.sched_labels', 0))
+
+    @torch.no_grad()
+    def xfc_forward(self, embed):
+        """Logits [B, num_labels] (chunked.py:48-53)."""
+        self._handle.bind([self.xfc_weight])
+        x = embed if embed.dtype in (torch.bfloat16, torch.float8_e4m3fn) else embed.to(torch.bfloat16)
+        out = torch.empty(x.shape[0], (self.num_labels + 7) // 8 * 8, dtype=torch.bfloat16, device=x.device)
+        self._handle.forward_logits(x.contiguous(), out, self.num_labels)
+        return out[:, :self.num_labels]
+
+    @torch.no_grad()
+    def xfc_forward_backward(self, embed, labels, xmc_lr, skip_loss=True):
+        """One train step of the layer (chunked.py:75-133): updates ``xfc_weight`` in place, leaves
+        the activation gradient in ``grad_input`` and returns the summed BCE loss (0 when skipped).
+
+        The bf16 reference materialises dW in bf16 (chunked.py:119) and applies no weight decay
+        (stochastic_rounding_kernel.py:91-99 ignores it); both are reproduced.
+        """
+        bsz = embed.shape[0]
+        if embed.dtype != self._dtype:
+            embed = embed.to(self._dtype)
+        self._handle.bind([self.xfc_weight])
+        self._handle.step(embed.contiguous(), as_labels(labels, embed.device), xmc_lr[0],
+                          wd=0.0, seed=self.base_seed, step=self.iteration,
+                          stochastic=(self.rounding == 'sr'), compute_loss=not skip_loss,
+                          round_dw_bf16=True, grad_bf16=self._grad_buf, loss_out=self._loss_dev)
+        self.grad_input = self._grad_buf[:bsz]
+        self.iteration += 1
+        return 0 if skip_loss else float(self._loss_dev.item())

@@ -1,0 +1,92 @@
+"""Counterpart of the reference's src/xmc_classifiers/chunked_fp8xmc_clf.py
+(Fp8XMCBCEChunkedLayer): e4m3 weight chunks in a ``ParameterList``, forward in FP8
+(``simulated_fp8``: bf16), backward contractions in bf16, SGD fused into the dW contraction.
+
+Same constructor ``(cfg)``, padding rule, attributes and methods as the reference.  New optional
+config keys (defaults reproduce the reference): ``training.xmc.rounding`` ('sr' | 'rn'),
+``training.xmc.w_scale`` (per-tensor scale, stored = real / w_scale), ``model.xmc.sched_labels``.
+"""
+import torch
+from torch import nn
+
+from ..handle import XmcHandle
+from ._common import as_labels, cfg_get, draw_base_seed
+
+
+class Fp8XMCBCEChunkedLayer(nn.Module):
+    def __init__(self, cfg):
+        super().__init__()
+        self.cfg = cfg
+        self.device = torch.device(cfg.environment.device)
+        self._dtype = torch.float8_e4m3fn
+        self.fake_fp8_matmul = cfg.training.xmc.simulated_fp8
+        self.num_chunks = cfg.model.xmc.num_chunks
+        # chunked_fp8xmc_clf.py:26-28: pad so that every chunk has a multiple of 16 rows
+        self.num_labels = cfg.data.num_labels + 16 * self.num_chunks - cfg.data.num_labels % (16 * self.num_chunks)
+        self.num_labels_i = self.num_labels // self.num_chunks
+        assert self.num_labels_i % 16 == 0
+        d = cfg.model.xmc.input_features
+        self.input_features = d
+        self.w_scale = float(cfg_get(cfg, 'training.xmc.w_scale', 1.0))
+        xfc_weight = torch.empty(self.num_labels, d, dtype=torch.float32)
+        nn.init.xavier_uniform_(xfc_weight)                                            # :29-30
+        if self.w_scale != 1.0:
+            xfc_weight /= self.w_scale
+        self.xfc_weight = nn.ParameterList([
+            nn.Parameter(xfc_weight[i * self.num_labels_i:(i + 1) * self.num_labels_i]
+                         .to(torch.float8_e4m3fn).to(self.device), requires_grad=False)
+            for i in range(self.num_chunks)])
+        self.block_size = 16
+        self.loss = torch.tensor(0.0, device=self.device)
+        self._loss_dev = torch.zeros(1, dtype=torch.float64, device=self.device)
+        self._grad_buf = torch.zeros(cfg.data.batch_size, d, dtype=torch.bfloat16, device=self.device)
+        self.grad_input = self._grad_buf
+        self.iteration = 0
+        self.rounding = cfg_get(cfg, 'training.xmc.rounding', 'sr')
+        self.base_seed = draw_base_seed()
+        self._handle = XmcHandle(self.device, d, cfg.data.batch_size,
+                                 'simfp8' if self.fake_fp8_matmul else 'fp8',
+                                 label_offset=cfg_get(cfg, 'model.xmc.label_offset', 0),
+                                 sched_labels=cfg_get(cfg, 'model.xmc.sched_labels', 0),
+                                 w_scale=self.w_scale)
+
+    def _weights(self):
+        return [p.data for p in self.xfc_weight]
+
+    @torch.no_grad()
+    def xfc_forward(self, embed):
+        """Logits [B, cfg.data.num_labels] bf16, padding rows hidden (:45-60).  ``embed`` may be
+        bf16 or already cast to e4m3 (the evaluator does that: src/evaluate.py:155-156)."""
+        self._handle.bind(self._weights())
+        n = self.cfg.data.num_labels
+        x = embed if embed.dtype in (torch.bfloat16, torch.float8_e4m3fn) else embed.to(torch.bfloat16)
+        out = torch.empty(x.shape[0], (n + 7) // 8 * 8, dtype=torch.bfloat16, device=x.device)
+        self._handle.forward_logits(x.contiguous(), out, n)
+        return out[:, :n]
+
+    @torch.no_grad()
+    def xfc_topk(self, embed, k):
+        """Fused ``xfc_forward`` + ``torch.topk`` (src/evaluate.py:158-159) without the logits."""
+        self._handle.bind(self._weights())
+        x = embed if embed.dtype in (torch.bfloat16, torch.float8_e4m3fn) else embed.to(torch.bfloat16)
+        return self._handle.forward_topk(x.contiguous(), k, self.cfg.data.num_labels)
+
+    @torch.no_grad()
+    def xfc_forward_backward(self, embed, labels, xmc_lr, skip_loss=True):
+        """One train step (:81-123).  The reference never computes the loss here (``skip_loss`` is
+        ignored and 0 returned); this class returns the summed BCE loss when ``skip_loss=False``."""
+        bsz = embed.shape[0]
+        if embed.dtype != torch.bfloat16:
+            embed = embed.to(torch.bfloat16)
+        self._handle.bind(self._weights())
+        self._handle.step(embed.contiguous(), as_labels(labels, embed.device), xmc_lr[0],
+                          seed=self.base_seed, step=self.iteration,
+                          stochastic=(self.rounding == 'sr'), compute_loss=not skip_loss,
+                          grad_bf16=self._grad_buf, loss_out=self._loss_dev)
+        self.iteration += 1
+        self.grad_input = self._grad_buf[:bsz]
+        return 0 if skip_loss else float(self._loss_dev.item())
+
+    def filter_non_local_inds(self, rows, cols, start, end):
+        mask = (cols >= start) & (cols < end)                                          # :124-126
+        return rows[mask], cols[mask] - start

@@ -1,0 +1,149 @@
+/*
+ * C ABI of the B200 (sm_100a) chunked XMC classifier layer.
+ *
+ * This is the boundary a binding of the reference (xmc-aalto/elmo, 100 % Python) would call
+ * through ctypes/cffi in place of its torch + Triton code.  Every function returns an int
+ * status (0 = XMC_OK); none throws, aborts or allocates through any framework.  All data
+ * pointers are DEVICE pointers owned by the caller unless stated otherwise; `stream` is a
+ * cudaStream_t passed as void* (NULL = legacy default stream).  Calls only enqueue work on
+ * `stream`; results are valid after the stream is synchronised.
+ *
+ * Reference interfaces replaced (paths relative to the reference's root):
+ *   xmc_create / xmc_bind_weights  src/xmc_classifiers/chunked.py:17-46,
+ *                                  src/xmc_classifiers/chunked_fp8xmc_clf.py:15-43 (constructors)
+ *   xmc_step                       chunked.py:75-133  xfc_forward_backward (bf16 weights)
+ *                                  chunked_fp8xmc_clf.py:81-123 xfc_forward_backward (e4m3
+ *                                  weights, real and simulated FP8), including its kernels
+ *                                  src/triton_kernels/matmul_kernel.py:204-239,342-353
+ *                                  (large_k_matmul), src/triton_kernels/fuse_kernel.py:63-131
+ *                                  (matmul_update), :134-199 (fakefp8_matmul_update),
+ *                                  src/triton_kernels/stochastic_rounding_kernel.py:65-99 (sgd_update)
+ *   xmc_forward_logits             chunked.py:48-53, chunked_fp8xmc_clf.py:45-60 xfc_forward
+ *   xmc_forward_topk               src/evaluate.py:158-159,235-236 (xfc_forward + torch.topk)
+ */
+#ifndef ELMO_XMC_H_
+#define ELMO_XMC_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes */
+enum {
+  XMC_OK = 0,
+  XMC_ERR_INVALID = 1,     /* bad argument (shape, alignment, enum)               */
+  XMC_ERR_CUDA = 2,        /* a CUDA runtime/driver call failed                   */
+  XMC_ERR_STATE = 3,       /* call order (weights not bound, ...)                 */
+  XMC_ERR_DEVICE_FLAG = 4  /* a kernel reported a bounded-wait time-out or a bad label */
+};
+
+/* element types */
+enum { XMC_DT_BF16 = 0, XMC_DT_E4M3 = 1, XMC_DT_F32 = 2 };
+
+/* arithmetic of the forward contraction */
+enum {
+  XMC_MODE_BF16 = 0,   /* bf16 weights, bf16 x bf16 contractions (reference 'chunked' in bfloat16)   */
+  XMC_MODE_FP8 = 1,    /* e4m3 weights, forward e4m3 x e4m3 (X cast to e4m3), backward in bf16        */
+  XMC_MODE_SIMFP8 = 2  /* e4m3 weights up-converted to bf16, all contractions bf16 ('simulated_fp8') */
+};
+
+/* flags of xmc_step */
+enum {
+  XMC_STEP_COMPUTE_LOSS = 1,      /* skip_loss == False: write the summed BCE loss             */
+  XMC_STEP_STOCHASTIC = 2,        /* stochastic rounding of W (else round-to-nearest-even)     */
+  XMC_STEP_ROUND_DW_BF16 = 4      /* round the dW accumulator to bf16 before the update, as the
+                                     reference's 'chunked' class does by materialising dW
+                                     (chunked.py:119)                                            */
+};
+
+typedef struct xmc_handle xmc_handle;
+
+typedef struct {
+  int32_t device;          /* CUDA device ordinal                                              */
+  int32_t dim;             /* d, features per label row; multiple of 16                        */
+  int32_t max_batch;       /* largest B a step will see (<= 65535)                             */
+  int32_t mode;            /* XMC_MODE_*                                                       */
+  int64_t label_offset;    /* global id of this handle's first label row (label-range shards)  */
+  int64_t sched_labels;    /* labels per scheduling chunk (multiple of 128); 0 = choose so that
+                              the chunk's logit-gradient tile stays L2 resident                */
+  float w_scale;           /* real weight = stored weight * w_scale (per-tensor, constant);
+                              1.0 reproduces the reference                                      */
+  int32_t reserved;
+} xmc_config;
+
+/* Create a handle and its workspaces on cfg->device (cudaMalloc; freed by xmc_destroy). */
+int xmc_create(const xmc_config* cfg, xmc_handle** out);
+int xmc_destroy(xmc_handle* h);
+
+/*
+ * Bind the weight storage: n_chunks row-major [rows[i] x dim] device arrays (bf16 in
+ * XMC_MODE_BF16, else e4m3), 16-byte aligned, borrowed -- never freed by the library.
+ * All chunks but the last must have the same number of rows.  The label rows of the handle are
+ * the concatenation of the chunks; row r of the concatenation has global id label_offset + r.
+ */
+int xmc_bind_weights(xmc_handle* h, int32_t n_chunks, void* const* ptrs, const int64_t* rows);
+
+/*
+ * One train step over all bound label rows:
+ *   Z = W X^T (per mode), G = sigmoid(Z) - Y, grad_X = w_scale * G^T W, W <- round(W - lr/w_scale * (G X)).
+ * x        [batch x dim], x_dtype XMC_DT_BF16, row-major, contiguous
+ * labels   int32 [nnz x 2] (batch row, GLOBAL label id); pairs outside this handle's label
+ *          range are ignored, duplicates count once; may be NULL when nnz == 0
+ * seed/step  Philox key / counter word for stochastic rounding
+ * grad_x_f32 fp32 [batch x dim] or NULL;  grad_x_bf16 bf16 [batch x dim] or NULL
+ * loss_out   device double, written when XMC_STEP_COMPUTE_LOSS is set (may be NULL otherwise)
+ */
+int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch,
+             const int32_t* labels, int64_t nnz, float lr, float wd,
+             uint64_t seed, uint64_t step, uint32_t flags,
+             float* grad_x_f32, void* grad_x_bf16, double* loss_out, void* stream);
+
+/*
+ * Logits of all bound rows: out[b, r] = bf16(w_scale * <W[r], x[b]>) for r < n_out
+ * (rows beyond n_out, e.g. the FP8 classes' padding, are not written).
+ * x_dtype XMC_DT_BF16 or XMC_DT_E4M3 (the reference's evaluator hands in e4m3-cast embeds).
+ * out is bf16 [batch x ld_out], ld_out >= n_out and a multiple of 8.
+ */
+int xmc_forward_logits(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch,
+                       void* out_bf16, int64_t ld_out, int64_t n_out, void* stream);
+
+/*
+ * Fused logits + per-row top-k over rows r < n_out, without materialising the logits:
+ * vals fp32 [batch x k] descending, idx int32 [batch x k] GLOBAL label ids
+ * (label_offset + r); ties go to the lower id.  k <= 128.
+ */
+int xmc_forward_topk(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, int32_t k,
+                     int64_t n_out, float* vals, int32_t* idx, void* stream);
+
+/*
+ * Synchronise `stream`, then read and clear the device status word.  Returns XMC_OK, or
+ * XMC_ERR_DEVICE_FLAG with details in xmc_last_error (bounded wait expired inside a kernel,
+ * label row >= batch, ...).
+ */
+int xmc_check(xmc_handle* h, void* stream);
+
+/* Bytes of device memory the handle allocated for itself (workspaces; not the weights). */
+int64_t xmc_workspace_bytes(const xmc_handle* h);
+
+/* Message of the most recent failing call on this thread ("" if none). */
+const char* xmc_last_error(void);
+
+/* Library build tag, e.g. "elmo_xmc sm_100a <date>". */
+const char* xmc_version(void);
+
+/*
+ * Test hook (not used by the layer classes): D[M x N] fp32 = A * B^T on the library's GEMM
+ * engine, to validate the tensor-core path in isolation.
+ *   layout 0: A [M x K], B [N x K] both K-major (row-major as written), dtype XMC_DT_BF16 or XMC_DT_E4M3
+ *   layout 1: A given as [K x M], B as [K x N] row-major (both "MN-major"), dtype XMC_DT_BF16
+ * M, N, K arbitrary positive (rows 16-byte aligned: inner extents multiples of 8 (bf16) / 16 (e4m3)).
+ */
+int xmc_test_gemm(int32_t device, int32_t layout, int32_t dtype, int32_t M, int32_t N, int32_t K,
+                  const void* A, const void* B, float* D, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ELMO_XMC_H_ */

@@ -1,0 +1,162 @@
+"""Parity of the CUDA train step (through the C ABI) with the CPU oracle on seeded inputs.
+
+Tolerances (the bar the task states): logits / grad_X within 1e-2 relative; updated weights
+bit-exact on >= 99.9 % of elements and never more than one grid step away; loss within 1e-3.
+"""
+import pytest
+import torch
+
+from tests._util import e4m3_ulp_distance, frac_equal_bits, rel_inf
+
+pytestmark = pytest.mark.gpu
+E4M3 = torch.float8_e4m3fn
+
+
+def _inputs(L, d, B, nnz, seed, w_std=0.25, w_dtype=E4M3, dup=True):
+    g = torch.Generator().manual_seed(seed)
+    w = (torch.randn(L, d, generator=g) * w_std).to(w_dtype)
+    x = (torch.randn(B, d, generator=g) / d ** 0.5).to(torch.bfloat16)
+    rows = torch.randint(0, B, (nnz,), generator=g)
+    cols = torch.randint(0, L, (nnz,), generator=g)
+    cols = torch.where(torch.rand(nnz, generator=g) < 0.4, cols % 5, cols)      # hot head labels
+    lab = torch.stack([rows, cols], 1).to(torch.int32)
+    if dup and nnz > 2:
+        lab = torch.cat([lab, lab[:2]], 0)                                      # duplicates: set semantics
+    return w, x, lab
+
+
+def _run_gpu(mode, chunks, x, lab, lr, *, stochastic, seed=5, step=0, loss=False, sched=0,
+             round_dw=False, w_scale=1.0, label_offset=0, max_batch=None):
+    from elmo_b200.handle import XmcHandle
+    dev = torch.device("cuda", 0)
+    d = x.shape[1]
+    h = XmcHandle(dev, d, max_batch or x.shape[0], mode, sched_labels=sched, w_scale=w_scale,
+                  label_offset=label_offset)
+    ws = [c.clone().cuda() for c in chunks]
+    h.bind(ws)
+    g32 = torch.zeros(x.shape[0], d, dtype=torch.float32, device=dev)
+    g16 = torch.zeros(x.shape[0], d, dtype=torch.bfloat16, device=dev)
+    lo = torch.zeros(1, dtype=torch.float64, device=dev)
+    h.step(x.cuda(), lab.cuda() if lab is not None else None, lr, seed=seed, step=step,
+           stochastic=stochastic, compute_loss=loss, round_dw_bf16=round_dw,
+           grad_f32=g32, grad_bf16=g16, loss_out=lo)
+    h.check()
+    out = [w.cpu() for w in ws], g32.cpu(), g16.cpu(), float(lo.item())
+    h.close()
+    return out
+
+
+def _check_weights(got, want, min_equal=0.999):
+    for a, b in zip(got, want):
+        assert a.shape == b.shape
+        f = frac_equal_bits(a, b)
+        assert f >= min_equal, f
+        if a.dtype == E4M3:
+            assert e4m3_ulp_distance(a, b) <= 1
+        else:
+            assert (a.float() - b.float()).abs().max() <= 2.0 ** -7 * b.float().abs().max()
+
+
+@pytest.mark.parametrize("rounding", ["rn", "sr"])
+@pytest.mark.parametrize("L,d,B,nc,sched", [(1024, 128, 48, 2, 256), (1040, 64, 16, 1, 0),
+                                            (4096, 768, 256, 2, 1024), (3000 - 8, 256, 512, 1, 512)])
+def test_fp8_step_matches_oracle(L, d, B, nc, sched, rounding):
+    from oracle import xmc_oracle as O
+    w, x, lab = _inputs(L, d, B, 6 * B, seed=L + B)
+    li = (L + nc - 1) // nc
+    li = (li + 15) // 16 * 16
+    chunks = [w[i * li:(i + 1) * li] for i in range(nc)]
+    want_w, want_gx, want_loss = O.fp8_chunked_step(chunks, x, lab, 0.5, rounding=rounding, seed=5, step=3,
+                                                    compute_loss=True)
+    got_w, g32, g16, loss = _run_gpu("fp8", chunks, x, lab, 0.5, stochastic=(rounding == "sr"), step=3,
+                                     loss=True, sched=sched)
+    _check_weights(got_w, want_w)
+    assert rel_inf(g32, want_gx) < 1e-2
+    assert rel_inf(g16, want_gx.to(torch.bfloat16)) < 1e-2
+    assert abs(loss - want_loss) < 1e-3 * abs(want_loss)
+    changed = sum(int((a.view(torch.uint8) != b.view(torch.uint8)).sum()) for a, b in zip(got_w, chunks))
+    assert changed > 0                                                # the step did update weights
+
+
+def test_fp8_step_with_scale_and_tiny_weights():
+    """Xavier-sized weights sit below e4m3's normal range at scale 1; with w_scale they train."""
+    from oracle import xmc_oracle as O
+    L, d, B = 2048, 128, 64
+    g = torch.Generator().manual_seed(1)
+    scale = 2.0 ** -8
+    w = ((torch.rand(L, d, generator=g) * 2 - 1) * 3e-3 / scale).to(E4M3)
+    _, x, lab = _inputs(L, d, B, 300, seed=2)
+    for rounding in ("rn", "sr"):
+        want_w, want_gx, want_loss = O.fp8_chunked_step([w], x, lab, 0.05, rounding=rounding, seed=5,
+                                                        w_scale=scale, compute_loss=True)
+        got_w, g32, _, loss = _run_gpu("fp8", [w], x, lab, 0.05, stochastic=(rounding == "sr"),
+                                       w_scale=scale, loss=True)
+        _check_weights(got_w, want_w)
+        assert rel_inf(g32, want_gx) < 1e-2
+        assert abs(loss - want_loss) < 1e-3 * abs(want_loss)
+
+
+@pytest.mark.parametrize("rounding", ["rn", "sr"])
+def test_simfp8_step_matches_oracle(rounding):
+    from oracle import xmc_oracle as O
+    L, d, B = 1536, 256, 80
+    w, x, lab = _inputs(L, d, B, 400, seed=9)
+    chunks = [w[:768], w[768:]]
+    want_w, want_gx, _ = O.fp8_chunked_step(chunks, x, lab, 0.5, simulated=True, rounding=rounding, seed=5)
+    got_w, g32, _, _ = _run_gpu("simfp8", chunks, x, lab, 0.5, stochastic=(rounding == "sr"), sched=512)
+    _check_weights(got_w, want_w)
+    assert rel_inf(g32, want_gx) < 1e-2
+
+
+@pytest.mark.parametrize("rounding", ["rn", "sr"])
+@pytest.mark.parametrize("L,d,B", [(1000, 64, 37), (2048, 768, 256)])
+def test_bf16_step_matches_oracle(L, d, B, rounding):
+    from oracle import xmc_oracle as O
+    w, x, lab = _inputs(L, d, B, 5 * B, seed=L, w_std=0.05, w_dtype=torch.bfloat16)
+    want_w, want_gx, want_loss = O.chunked_step(w, x, lab, 0.5, num_chunks=3, rounding=rounding, seed=5,
+                                                step=1, compute_loss=True)
+    got_w, g32, _, loss = _run_gpu("bf16", [w], x, lab, 0.5, stochastic=(rounding == "sr"), step=1,
+                                   loss=True, round_dw=True, sched=512)
+    _check_weights(got_w, [want_w], min_equal=0.995)
+    assert rel_inf(g32, want_gx) < 1e-2
+    assert abs(loss - want_loss) < 1e-3 * abs(want_loss)
+
+
+def test_empty_labels_and_foreign_labels_are_ignored():
+    from oracle import xmc_oracle as O
+    L, d, B = 512, 64, 16
+    w, x, _ = _inputs(L, d, B, 10, seed=4)
+    empty = torch.zeros(0, 2, dtype=torch.int32)
+    want_w, want_gx, _ = O.fp8_chunked_step([w], x, empty, 0.5, rounding="rn")
+    got_w, g32, _, _ = _run_gpu("fp8", [w], x, None, 0.5, stochastic=False)
+    _check_weights(got_w, want_w)
+    assert rel_inf(g32, want_gx) < 1e-2
+    # a shard that owns labels [1000, 1512): ids outside are other shards' business
+    lab = torch.tensor([[0, 3], [1, 1000], [2, 1511], [3, 1512], [3, 99999]], dtype=torch.int32)
+    want_w, want_gx, _ = O.fp8_chunked_step([w], x, lab, 0.5, rounding="rn", label_offset=1000)
+    got_w, g32, _, _ = _run_gpu("fp8", [w], x, lab, 0.5, stochastic=False, label_offset=1000)
+    _check_weights(got_w, want_w)
+    assert rel_inf(g32, want_gx) < 1e-2
+
+
+def test_bad_label_row_is_reported_not_fatal():
+    from elmo_b200._lib import XmcError
+    L, d, B = 256, 64, 16
+    w, x, _ = _inputs(L, d, B, 10, seed=4)
+    lab = torch.tensor([[0, 3], [16, 5]], dtype=torch.int32)         # row 16 >= batch
+    with pytest.raises(XmcError):
+        _run_gpu("fp8", [w], x, lab, 0.5, stochastic=False)
+    # the context is still usable afterwards
+    got_w, _, _, _ = _run_gpu("fp8", [w], x, lab[:1], 0.5, stochastic=False)
+    assert got_w[0].shape == w.shape
+
+
+def test_two_steps_are_deterministic_and_use_fresh_bits():
+    L, d, B = 1024, 128, 32
+    w, x, lab = _inputs(L, d, B, 100, seed=21)
+    a = _run_gpu("fp8", [w], x, lab, 0.5, stochastic=True, step=0)
+    b = _run_gpu("fp8", [w], x, lab, 0.5, stochastic=True, step=0)
+    c = _run_gpu("fp8", [w], x, lab, 0.5, stochastic=True, step=1)
+    assert torch.equal(a[0][0].view(torch.uint8), b[0][0].view(torch.uint8))
+    assert torch.equal(a[1], b[1])                                    # grad_X bit-reproducible
+    assert not torch.equal(a[0][0].view(torch.uint8), c[0][0].view(torch.uint8))
