@@ -130,6 +130,12 @@ struct xmc_handle {
   int64_t loss_cap = 0;
   int* status = nullptr;           // 4 ints
   int64_t ws_bytes = 0;
+  // bookkeeping for the bench: kernels launched so far, optional per-kernel-class event timing
+  int64_t launches = 0;
+  bool profile = false;
+  std::vector<cudaEvent_t> ev_pool;
+  std::vector<int> ev_kind;        // kind of the kernel that FOLLOWS event i
+  size_t ev_used = 0;
 };
 
 namespace {
@@ -154,6 +160,22 @@ struct DeviceGuard {
   }
 };
 
+// Count a kernel launch; in profile mode also drop an event in front of it.
+enum { K_PREP = 0, K_CONVERT = 1, K_FWD = 2, K_GRADX = 3, K_UPD = 4, K_REDUCE = 5, K_LOGITS = 6, K_END = 7 };
+void mark(xmc_handle* h, int kind, cudaStream_t st) {
+  if (kind != K_END) ++h->launches;
+  if (!h->profile) return;
+  if (h->ev_used == h->ev_pool.size()) {
+    cudaEvent_t e;
+    if (cudaEventCreate(&e) != cudaSuccess) return;
+    h->ev_pool.push_back(e);
+    h->ev_kind.push_back(kind);
+  }
+  h->ev_kind[h->ev_used] = kind;
+  cudaEventRecord(h->ev_pool[h->ev_used], st);
+  ++h->ev_used;
+}
+
 xmc::BucketGeom geom_of(const xmc_handle* h) {
   xmc::BucketGeom g;
   g.label_offset = h->cfg.label_offset;
@@ -169,6 +191,7 @@ int prep_x(xmc_handle* h, const void* x, int x_dtype, int batch, int bpad, bool 
            bool need_xt, cudaStream_t st) {
   const int d = h->cfg.dim;
   dim3 grid(cdiv(d, 32), cdiv(bpad, 32)), block(32, 8);
+  mark(h, K_PREP, st);
   if (x_dtype == XMC_DT_E4M3)
     xmc::prep_x_kernel<true><<<grid, block, 0, st>>>(x, batch, bpad, d, need_x8 ? h->x8 : nullptr,
                                                      need_x16 ? h->x16 : nullptr, need_xt ? h->xt : nullptr);
@@ -243,6 +266,7 @@ int xmc_destroy(xmc_handle* h) {
                   h->entries, h->loss_partial, h->status};
   for (void* p : ptrs)
     if (p != nullptr) cudaFree(p);
+  for (cudaEvent_t e : h->ev_pool) cudaEventDestroy(e);
   delete h;
   return XMC_OK;
 }
@@ -332,12 +356,15 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
   const xmc::BucketGeom geom = geom_of(h);
   CU_TRY(cudaMemsetAsync(h->bucket_cnt, 0, (size_t)h->n_buckets * 8, st));
   if (nnz > 0) {
+    mark(h, K_PREP, st);
     xmc::bucket_count_kernel<<<cdiv(nnz, 256), 256, 0, st>>>(labels, nnz, batch, geom, h->bucket_cnt, h->status);
     CU_TRY(cudaGetLastError());
   }
+  mark(h, K_PREP, st);
   xmc::bucket_scan_kernel<<<1, 1024, 0, st>>>(h->bucket_cnt, h->n_buckets, h->bucket_off);
   CU_TRY(cudaGetLastError());
   if (nnz > 0) {
+    mark(h, K_PREP, st);
     xmc::bucket_fill_kernel<<<cdiv(nnz, 256), 256, 0, st>>>(labels, nnz, batch, geom, h->bucket_off,
                                                             h->bucket_cnt + h->n_buckets, h->entries);
     CU_TRY(cudaGetLastError());
@@ -382,6 +409,7 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
       if (w8) {
         const long long n16 = (long long)rows_valid * d / 16;
         const int blocks = (int)std::min<long long>((n16 + 255) / 256, (long long)h->sm_count * 8);
+        mark(h, K_CONVERT, st);
         xmc::e4m3_to_bf16_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const uint4*>(wbase),
                                                          reinterpret_cast<uint4*>(h->w16), n16);
         CU_TRY(cudaGetLastError());
@@ -415,6 +443,7 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
         CU_TRY(cudaMemsetAsync(fp.loss_partial, 0, (size_t)h->sm_count * 4 * sizeof(double), st));
       }
       int rc;
+      mark(h, K_FWD, st);
       if (fwd_fp8) rc = want_loss ? launch_gemm<xmc::FwdPolicy<true, true>>(map_w, map_x, fp, f_tiles, h->sm_count, st)
                                   : launch_gemm<xmc::FwdPolicy<true, false>>(map_w, map_x, fp, f_tiles, h->sm_count, st);
       else rc = want_loss ? launch_gemm<xmc::FwdPolicy<false, true>>(map_w, map_x, fp, f_tiles, h->sm_count, st)
@@ -434,6 +463,7 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
       gp.accumulate = first ? 0 : 1;
       gp.partial = h->partial;
       gp.status = h->status;
+      mark(h, K_GRADX, st);
       if ((rc = launch_gemm<xmc::GradXPolicy>(map_g_mn, map_w_mn, gp, n_bt * n_dt * n_splits, h->sm_count, st))) return rc;
 
       // fused dW + SGD update of the chunk, in place
@@ -452,6 +482,7 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
       up.round_dw_bf16 = (flags & XMC_STEP_ROUND_DW_BF16) ? 1 : 0;
       up.status = h->status;
       const int u_tiles = n_lt * n_dt;
+      mark(h, K_UPD, st);
       if (w8) rc = sr ? launch_gemm<xmc::UpdPolicy<true, true>>(map_g_k, map_xt, up, u_tiles, h->sm_count, st)
                       : launch_gemm<xmc::UpdPolicy<true, false>>(map_g_k, map_xt, up, u_tiles, h->sm_count, st);
       else rc = sr ? launch_gemm<xmc::UpdPolicy<false, true>>(map_g_k, map_xt, up, u_tiles, h->sm_count, st)
@@ -466,14 +497,39 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
   if (grad_x_f32 != nullptr || grad_x_bf16 != nullptr) {
     const long long n = (long long)batch * d;
     const int blocks = (int)std::min<long long>((n + 255) / 256, (long long)h->sm_count * 8);
+    mark(h, K_REDUCE, st);
     xmc::reduce_gradx_kernel<<<blocks, 256, 0, st>>>(h->partial, n_splits, batch, bpad, d, h->cfg.w_scale,
                                                      grad_x_f32, reinterpret_cast<__nv_bfloat16*>(grad_x_bf16));
     CU_TRY(cudaGetLastError());
   }
   if (want_loss) {
+    mark(h, K_REDUCE, st);
     xmc::reduce_loss_kernel<<<1, 32, 0, st>>>(h->loss_partial, launch_idx * h->sm_count * 4, loss_out);
     CU_TRY(cudaGetLastError());
   }
+  mark(h, K_END, st);
+  return XMC_OK;
+}
+
+int64_t xmc_launch_count(const xmc_handle* h) { return h ? h->launches : 0; }
+
+int xmc_profile(xmc_handle* h, int32_t enable, double* ms_by_kind, int64_t* launches_by_kind) {
+  if (h == nullptr) return fail(XMC_ERR_INVALID, "null handle");
+  DeviceGuard guard(h->cfg.device);
+  if (ms_by_kind != nullptr && launches_by_kind != nullptr) {
+    for (int k = 0; k < 8; ++k) { ms_by_kind[k] = 0.0; launches_by_kind[k] = 0; }
+    if (h->ev_used > 0) CU_TRY(cudaEventSynchronize(h->ev_pool[h->ev_used - 1]));
+    for (size_t i = 0; i + 1 < h->ev_used; ++i) {
+      const int kind = h->ev_kind[i];
+      if (kind == K_END) continue;
+      float ms = 0.f;
+      CU_TRY(cudaEventElapsedTime(&ms, h->ev_pool[i], h->ev_pool[i + 1]));
+      ms_by_kind[kind] += ms;
+      launches_by_kind[kind] += 1;
+    }
+  }
+  h->ev_used = 0;
+  h->profile = enable != 0;
   return XMC_OK;
 }
 

@@ -113,6 +113,23 @@ class XmcHandle:
                                              _ptr(vals), _ptr(idx), self._stream()))
         return vals, idx
 
+    @property
+    def launch_count(self) -> int:
+        return int(self.lib.xmc_launch_count(self._h))
+
+    KINDS = ("prep", "stage_w", "forward", "grad_x", "update", "reduce", "logits", "unused")
+
+    def profile(self, enable: bool, read: bool = False):
+        """Switch per-kernel-class event timing on/off; with ``read`` return
+        {class: (ms, launches)} accumulated since the last call."""
+        if read:
+            ms = (C.c_double * 8)()
+            cnt = (C.c_int64 * 8)()
+            _lib.check(self.lib.xmc_profile(self._h, int(enable), ms, cnt))
+            return {k: (ms[i], cnt[i]) for i, k in enumerate(self.KINDS) if cnt[i]}
+        _lib.check(self.lib.xmc_profile(self._h, int(enable), None, None))
+        return None
+
     def check(self):
         """Synchronise the current stream and raise if a kernel flagged an error."""
         _lib.check(self.lib.xmc_check(self._h, self._stream()))

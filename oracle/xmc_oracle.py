@@ -150,6 +150,30 @@ def sr_bf16(w: np.ndarray, r16: np.ndarray) -> np.ndarray:
     return bits.view(np.float32).copy()
 
 
+_CLIB = False
+
+
+def _c_lib():
+    """oracle/sr_philox.c compiled (same definitions as the numpy statements above, only faster);
+    None when gcc is unavailable -- the numpy path is then used."""
+    global _CLIB
+    if _CLIB is False:
+        try:
+            import ctypes as C
+            from . import build_c
+            lib = C.CDLL(build_c.build())
+            for name in ("oracle_sr_e4m3", "oracle_sr_bf16"):
+                getattr(lib, name).argtypes = [C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64,
+                                               C.c_void_p]
+                getattr(lib, name).restype = None
+            lib.oracle_sr_bits16.argtypes = [C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_void_p]
+            lib.oracle_sr_bits16.restype = None
+            _CLIB = lib
+        except Exception:
+            _CLIB = None
+    return _CLIB
+
+
 def round_update(w32: torch.Tensor, w_dtype: torch.dtype, rounding: str,
                  seed: int, step: int, first_elem: int) -> torch.Tensor:
     """Round the fp32 updated weights ``w32`` [rows, d] to ``w_dtype``.
@@ -162,6 +186,14 @@ def round_update(w32: torch.Tensor, w_dtype: torch.dtype, rounding: str,
             return cast_e4m3_sat(w32)
         return w32.to(w_dtype)
     n = w32.numel()
+    clib = _c_lib()
+    if clib is not None and rounding == 'sr' and w_dtype in (E4M3, torch.bfloat16):
+        src = w32.detach().to(torch.float32).contiguous()
+        out = torch.empty_like(src)
+        fn = clib.oracle_sr_e4m3 if w_dtype == E4M3 else clib.oracle_sr_bf16
+        fn(src.data_ptr(), n, int(first_elem), int(seed) & (2 ** 64 - 1), int(step) & (2 ** 64 - 1),
+           out.data_ptr())
+        return out.to(w_dtype)                          # exact: values already on the grid
     idx = np.arange(first_elem, first_elem + n, dtype=np.uint64).reshape(w32.shape)
     r16 = philox.sr_bits16(idx, seed, step)
     wn = w32.detach().to(torch.float32).contiguous().numpy()

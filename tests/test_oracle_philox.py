@@ -79,3 +79,21 @@ def test_sharded_equals_unsharded():
         assert torch.equal(torch.cat(parts).view(torch.uint8), full)
         assert torch.allclose(gxs, gx, rtol=1e-5, atol=1e-6)
         assert abs(ls - loss) < 1e-6 * abs(loss)
+
+
+def test_c_restatement_equals_numpy_statements():
+    lib = O._c_lib()
+    assert lib is not None, "gcc build of oracle/sr_philox.c failed"
+    n, first, seed, step = 5000, 8 * 777 + 3, 0xDEADBEEF12345678, 2 ** 33 + 5
+    bits = np.empty(n, dtype=np.uint32)
+    lib.oracle_sr_bits16(first, n, seed, step, bits.ctypes.data)
+    idx = np.arange(first, first + n, dtype=np.uint64)
+    assert np.array_equal(bits, philox.sr_bits16(idx, seed, step))
+    rng = np.random.default_rng(0)
+    w = (rng.standard_normal(n) * np.exp(rng.uniform(-12, 7, n))).astype(np.float32)
+    w[:4] = [0.0, -0.0, 1e9, np.nan]
+    wt = torch.from_numpy(w).reshape(50, 100)
+    for dt, fn in ((O.E4M3, O.sr_e4m3_exact), (torch.bfloat16, O.sr_bf16)):
+        got = O.round_update(wt, dt, "sr", seed, step, first).to(torch.float32).numpy().ravel()
+        want = torch.from_numpy(fn(w, bits)).to(dt).to(torch.float32).numpy()
+        assert np.array_equal(got, want, equal_nan=True)

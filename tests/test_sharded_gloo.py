@@ -1,0 +1,85 @@
+"""World-size-2 CPU (gloo) test of the label-sharding plumbing: gather of embeddings and padded
+labels, shard-local step (the CPU oracle stands in for the CUDA engine), reduce-scatter of grad_X.
+The sharded result must equal the unsharded oracle step."""
+import os
+import socket
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from elmo_b200.sharded import LabelShardedXMC, pad_labels, shard_bounds
+
+L, D, B_LOC, WORLD = 416, 32, 8, 2
+
+
+class OracleEngine:
+    def __init__(self, weights, label_offset):
+        self.weights, self.label_offset = weights, label_offset
+
+    def step(self, x, labels, lr, seed, step, stochastic, grad_f32, compute_loss=False, loss_out=None):
+        from oracle import xmc_oracle as O
+        new, gx, _ = O.fp8_chunked_step(self.weights, x, labels, lr, rounding="sr" if stochastic else "rn",
+                                        seed=seed, step=step, label_offset=self.label_offset)
+        for w, n in zip(self.weights, new):
+            w.copy_(n)
+        grad_f32.copy_(gx)
+
+
+def _data():
+    g = torch.Generator().manual_seed(0)
+    w = (torch.randn(L, D, generator=g) * 0.25).to(torch.float8_e4m3fn)
+    xs, labs = [], []
+    for r in range(WORLD):
+        xs.append((torch.randn(B_LOC, D, generator=g) / D ** 0.5).to(torch.bfloat16))
+        n = 5 + 3 * r
+        labs.append(torch.stack([torch.randint(0, B_LOC, (n,), generator=g),
+                                 torch.randint(0, L, (n,), generator=g)], 1).to(torch.int32))
+    return w, xs, labs
+
+
+def _worker(rank, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=WORLD)
+    try:
+        w, xs, labs = _data()
+        lo, hi = shard_bounds(L, WORLD)[rank]
+        mine = [w[lo:hi].clone()]
+        layer = LabelShardedXMC(OracleEngine(mine, lo), dim=D, local_batch=B_LOC, num_rows=L,
+                                label_capacity=16, base_seed=9, rounding="sr")
+        for it in range(2):
+            layer.xfc_forward_backward(xs[rank], labs[rank], [0.5])
+        out[rank] = (mine[0].view(torch.uint8).clone(), layer.grad_input.float().clone())
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_sharded_step_equals_unsharded():
+    from oracle import xmc_oracle as O
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_worker, args=(port, out), nprocs=WORLD, join=True)
+    w, xs, labs = _data()
+    x = torch.cat(xs)
+    lab = torch.cat([torch.stack([l[:, 0] + r * B_LOC, l[:, 1]], 1) for r, l in enumerate(labs)]).to(torch.int32)
+    chunks = [w]
+    for it in range(2):
+        chunks, gx, _ = O.fp8_chunked_step(chunks, x, lab, 0.5, rounding="sr", seed=9, step=it)
+    full = chunks[0].view(torch.uint8)
+    for r, (lo, hi) in enumerate(shard_bounds(L, WORLD)):
+        w_r, g_r = out[r]
+        assert torch.equal(w_r, full[lo:hi])
+        want = gx[r * B_LOC:(r + 1) * B_LOC].to(torch.bfloat16).float()
+        assert torch.allclose(g_r, want, rtol=2e-2, atol=1e-6)
+
+
+def test_pad_labels_and_bounds():
+    lab = torch.tensor([[1, 7], [2, 9]], dtype=torch.int32)
+    p = pad_labels(lab, 4, 10, "cpu")
+    assert p.tolist() == [[11, 7], [12, 9], [0, 2 ** 31 - 1], [0, 2 ** 31 - 1]]
+    assert pad_labels(None, 2, 0, "cpu")[:, 1].tolist() == [2 ** 31 - 1] * 2
+    b = shard_bounds(670208, 8)
+    assert b[0][0] == 0 and b[-1][1] == 670208 and all(lo % 16 == 0 for lo, _ in b)
+    assert all(b[i][1] == b[i + 1][0] for i in range(7))
+    assert shard_bounds(100, 8)[-1] == (100, 100)          # trailing ranks may own nothing
