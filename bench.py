@@ -99,9 +99,10 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def layer_cfg(wl, device, batch, num_labels=None, num_chunks=None):
+def layer_cfg(wl, device, batch, num_labels=None, num_chunks=None, sched=0):
     return NS(environment=NS(device=str(device)),
-              model=NS(xmc=NS(dtype="bfloat16", num_chunks=num_chunks or wl.num_chunks, input_features=wl.dim)),
+              model=NS(xmc=NS(dtype="bfloat16", num_chunks=num_chunks or wl.num_chunks, input_features=wl.dim,
+                              sched_labels=sched)),
               training=NS(precision=NS(mode="mixed", purelp_dtype="bfloat16"),
                           xmc=NS(momentum=0, wd=0.0, simulated_fp8=(wl.mode == "simfp8"), rounding=wl.rounding),
                           FP8=NS(using_head_kahan=False, fp8_head_kahan=False, head_ratio=0.0)),
@@ -230,7 +231,7 @@ def run_ours(args, wl, rank, local_rank, world):
     cap = max(int(l.shape[0]) for _, l in pool) + 64
 
     if world == 1:
-        layer = Fp8XMCBCEChunkedLayer(layer_cfg(wl, device, b_loc))
+        layer = Fp8XMCBCEChunkedLayer(layer_cfg(wl, device, b_loc, sched=args.sched))
         fill_weights([p.data for p in layer.xfc_weight], wl.dim, seed=0)
         handle = layer._handle
         n_rows = layer.num_labels
@@ -242,7 +243,7 @@ def run_ours(args, wl, rank, local_rank, world):
         lo, hi = shard_bounds(n_rows, world)[rank]
         w = torch.empty(hi - lo, wl.dim, dtype=torch.float8_e4m3fn, device=device)
         fill_weights([w], wl.dim, seed=rank)
-        engine = CudaShardEngine(device, wl.dim, B, wl.mode, lo, [w])
+        engine = CudaShardEngine(device, wl.dim, B, wl.mode, lo, [w], sched_labels=args.sched)
         cap = b_loc * 64
         layer = LabelShardedXMC(engine, dim=wl.dim, local_batch=b_loc, num_rows=n_rows, label_capacity=cap,
                                 device=device, base_seed=1234, rounding=wl.rounding)
@@ -319,7 +320,7 @@ def run_ours(args, wl, rank, local_rank, world):
         "step_tflops": total_flops / (step_ms * 1e-3) / 1e12,
         "peak_hbm_gb_per_gpu": peak_hbm,
     }
-    if world == 1:
+    if world == 1 and not args.no_cpu:
         cpu, _ = cpu_step_sample(wl, 8192, reps_budget_s=12.0)
         out["cpu_baseline"] = cpu
     print(json.dumps(out))
@@ -328,13 +329,25 @@ def run_ours(args, wl, rank, local_rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(synth.WORKLOADS))
+    ap.add_argument("--sched", type=int, default=0, help="labels per scheduling chunk (0 = library default)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (tuning runs)")
+    ap.add_argument("--rounding", default="", choices=["", "rn", "sr"], help="override the rounding mode")
+    ap.add_argument("--labels", type=int, default=0, help="override the label count (small profiling captures)")
+    ap.add_argument("--batch", type=int, default=0, help="override the per-rank batch")
     args = ap.parse_args()
     rank, local_rank, world = env_int("RANK", 0), env_int("LOCAL_RANK", 0), env_int("WORLD_SIZE", 1)
     wl = synth.WORKLOADS[args.workload]
+    if args.labels or args.batch:
+        import dataclasses
+        wl = dataclasses.replace(wl, name=wl.name + "-resized", num_labels=args.labels or wl.num_labels,
+                                 batch=args.batch or wl.batch)
+    if args.rounding:
+        import dataclasses
+        wl = dataclasses.replace(wl, rounding=args.rounding)
     if args.impl == "reference":
         run_reference(args, wl, rank, world)
     else:

@@ -2,7 +2,8 @@
 //
 //   warp 0      TMA producer   (one elected lane): global -> shared ring of kStages slots
 //   warp 1      MMA issuer     (one elected lane): tcgen05.mma, shared -> TMEM accumulator
-//   warps 2..5  epilogue       (128 threads = 128 TMEM lanes): TMEM -> registers -> policy
+//   warps 2..   epilogue       (kEpiWarps/4 warps per 32-lane TMEM quarter, interleaved 32-column groups):
+//                              TMEM -> registers -> policy
 //
 // One CTA per SM (the shared-memory request forbids a second one, which also keeps the 512-column
 // TMEM allocation from ever blocking).  The accumulator is double buffered (2 x 256 columns) so the
@@ -14,8 +15,7 @@
 
 namespace xmc {
 
-constexpr int kNumThreads = 192;
-constexpr int kEpilogueThreads = 128;
+constexpr int kMaxEpiWarps = 16;            // a policy picks 4, 8 or 16 epilogue warps (kEpiWarps)
 constexpr int kStages = 4;
 constexpr int kTileM = 128;                 // UMMA M = TMEM lanes
 constexpr int kTileN = 256;                 // UMMA N upper bound = TMEM columns per accumulator
@@ -35,6 +35,14 @@ struct Job {
   int t0, t1, t2;  // policy-defined tile coordinates
 };
 
+struct EpiCtx {
+  int q;        // TMEM lane quarter: rows q*32 .. q*32+31 of the tile
+  int lane;
+  int h;        // this warp handles 32-column groups h, h+nsplit, h+2*nsplit, ...
+  int nsplit;
+  int slot;     // epilogue warp index 0..kEpiWarps-1
+};
+
 struct SharedTail {
   uint64_t full[kStages];
   uint64_t empty[kStages];
@@ -48,7 +56,7 @@ struct SharedTail {
 constexpr int kSmemBytes = kStages * kStageBytes + (int)sizeof(SharedTail) + 1024;
 
 template <class Policy>
-__global__ void __launch_bounds__(kNumThreads, 1)
+__global__ void __launch_bounds__(64 + 32 * Policy::kEpiWarps, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
             const typename Policy::Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -66,7 +74,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&sh.tmem_full[b]), 1);
-      mbar_init(smem_u32(&sh.tmem_empty[b]), kEpilogueThreads);
+      mbar_init(smem_u32(&sh.tmem_empty[b]), 32 * Policy::kEpiWarps);
     }
     sh.ctl.abort = 0;
     fence_barrier_init();
@@ -169,7 +177,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     // ------------------------------ epilogue ------------------------------
     // No block-level barrier is used in here: a warp that unwinds after a time-out must never
     // leave the others stuck in an unbounded bar.sync.  Warps cooperate through __syncwarp only.
-    const int q = warp & 3;                         // TMEM lane quarter this warp may access
+    EpiCtx ec;
+    ec.q = warp & 3;                                // TMEM lane quarter this warp may access
+    ec.lane = lane;
+    ec.h = (warp - 2) >> 2;                         // which of the column-group phases this warp takes
+    ec.nsplit = Policy::kEpiWarps / 4;
+    ec.slot = warp - 2;
+    const int q = ec.q;
     typename Policy::EpilogueState st;
     Policy::epilogue_begin(p, st);
     uint32_t t_local = 0;
@@ -177,15 +191,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       Job job;
       Policy::job(p, tile, job);
       const uint32_t buf = t_local & 1u, aph = (t_local >> 1) & 1u;
-      Policy::epilogue_pre(p, job, sh, q, lane, st);          // overlaps the tile's main loop
+      Policy::epilogue_pre(p, job, sh, ec, st);          // overlaps the tile's main loop
       if (!mbar_wait(smem_u32(&sh.tmem_full[buf]), aph, &sh.ctl, p.status, 400 + (int)buf)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * kTileN;
-      Policy::epilogue(p, job, taddr, job.k_steps > 0, sh, q, lane, st);
+      Policy::epilogue(p, job, taddr, job.k_steps > 0, sh, ec, st);
       tc_fence_before();
       mbar_arrive(smem_u32(&sh.tmem_empty[buf]));
     }
-    Policy::epilogue_end(p, sh, q, lane, st);
+    Policy::epilogue_end(p, sh, ec, st);
   }
 
   __syncwarp();

@@ -11,6 +11,13 @@ namespace xmc {
 __device__ __forceinline__ float bf16_round(float x) {
   return __bfloat162float(__float2bfloat16_rn(x));
 }
+// Same rounding (nearest-even, NaN kept quiet) with integer ALU ops only: float<->bf16 cvt
+// instructions share the special-function pipe with ex2/rcp, which the forward epilogue saturates.
+__device__ __forceinline__ float bf16_round_alu(float x) {
+  const uint32_t u = __float_as_uint(x);
+  const uint32_t r = (u + 0x7FFFu + ((u >> 16) & 1u)) & 0xFFFF0000u;
+  return __uint_as_float((u & 0x7FFFFFFFu) > 0x7F800000u ? (u | 0x00400000u) & 0xFFFF0000u : r);
+}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -27,6 +34,14 @@ __device__ __forceinline__ uint16_t float2_to_e4m3x2(float x, float y) {
   return (uint16_t)__nv_cvt_float2_to_fp8x2(make_float2(x, y), __NV_SATFINITE, __NV_E4M3);
 }
 
+// 1 / (1 + 2^(-z log2 e)) with the two approximate special-function ops (relative error ~2^-22,
+// far below the bf16 rounding that follows)
+__device__ __forceinline__ float fast_sigmoid(float z) {
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(z * -1.4426950408889634f));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return r;
+}
 // sigmoid of a bf16-valued float, rounded back to bf16 (the reference applies torch.sigmoid in
 // place on bf16 logits: chunked.py:112, chunked_fp8xmc_clf.py:107)
 __device__ __forceinline__ float sigmoid_bf16(float z) {
@@ -61,15 +76,13 @@ __device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint2 k) {
 // trick, fuse_kernel.py:28-36).  Below 2^-6 the grid is uniform (step 2^-9): shift the value into
 // the binade [2^-6, 2^-5), whose 3-bit step is 2^-9, round there and shift back (both exact).
 __device__ __forceinline__ float sr_e4m3(float w, uint32_t r16) {
-  if (w != w) return w;
-  float a = fminf(fabsf(w), 448.0f);
-  const bool small = a < 0.015625f;
-  float y = small ? a + 0.015625f : a;
-  uint32_t bits = (__float_as_uint(y) + (r16 << 4)) & 0xFFF00000u;
-  y = __uint_as_float(bits);
-  if (small) y -= 0.015625f;
-  y = fminf(y, 448.0f);
-  return copysignf(y, w);
+  // branch-free: this runs for every weight element, interleaved across elements by the scheduler
+  const float a = fminf(fabsf(w), 448.0f);               // fminf drops a NaN operand; restored below
+  const float off = a < 0.015625f ? 0.015625f : 0.0f;
+  const uint32_t bits = (__float_as_uint(a + off) + (r16 << 4)) & 0xFFF00000u;
+  const float y = fminf(__uint_as_float(bits) - off, 448.0f);
+  const float out = copysignf(y, w);
+  return w != w ? w : out;
 }
 // Stochastic rounding onto the bf16 grid: add 16 random bits below the kept mantissa, truncate
 // (fuse_kernel.py:10-17).  Returns the bf16 bit pattern.

@@ -94,7 +94,7 @@ int launch_gemm(const CUtensorMap& a, const CUtensorMap& b, const typename Polic
   // per device and cheap; one process may drive several devices
   CU_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, xmc::kSmemBytes));
   const int grid = std::min(n_tiles, sm_count);
-  kern<<<grid, xmc::kNumThreads, xmc::kSmemBytes, stream>>>(a, b, p);
+  kern<<<grid, 64 + 32 * Policy::kEpiWarps, xmc::kSmemBytes, stream>>>(a, b, p);
   CU_TRY(cudaGetLastError());
   return XMC_OK;
 }
@@ -298,7 +298,7 @@ int xmc_bind_weights(xmc_handle* h, int32_t n_chunks, void* const* ptrs, const i
     h->n_buckets = nb;
     if (int rc = dev_alloc(h, (void**)&h->bucket_cnt, (size_t)nb * 8, true)) return rc;
     if (int rc = dev_alloc(h, (void**)&h->bucket_off, (size_t)(nb + 1) * 4, true)) return rc;
-    h->loss_cap = (int64_t)n_chunks * spc * h->sm_count * 4;
+    h->loss_cap = (int64_t)n_chunks * spc * h->sm_count * xmc::kMaxEpiWarps;
     if (int rc = dev_alloc(h, (void**)&h->loss_partial, (size_t)h->loss_cap * 8, true)) return rc;
   }
   return XMC_OK;
@@ -435,12 +435,12 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
       fp.bucket_off = h->bucket_off;
       fp.bucket_ent = h->entries;
       fp.tile_base = ((int)wc * spc + sc) * tiles_per_sched;
-      fp.loss_partial = want_loss ? h->loss_partial + (size_t)launch_idx * h->sm_count * 4 : nullptr;
+      fp.loss_partial = want_loss ? h->loss_partial + (size_t)launch_idx * h->sm_count * xmc::kMaxEpiWarps : nullptr;
       fp.status = h->status;
       const int f_tiles = fp.n_ltiles * fp.n_btiles;
       if (want_loss && std::min(f_tiles, h->sm_count) < h->sm_count) {
         // slots of CTAs that are not launched must read as zero
-        CU_TRY(cudaMemsetAsync(fp.loss_partial, 0, (size_t)h->sm_count * 4 * sizeof(double), st));
+        CU_TRY(cudaMemsetAsync(fp.loss_partial, 0, (size_t)h->sm_count * xmc::kMaxEpiWarps * sizeof(double), st));
       }
       int rc;
       mark(h, K_FWD, st);
@@ -483,10 +483,21 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
       up.status = h->status;
       const int u_tiles = n_lt * n_dt;
       mark(h, K_UPD, st);
-      if (w8) rc = sr ? launch_gemm<xmc::UpdPolicy<true, true>>(map_g_k, map_xt, up, u_tiles, h->sm_count, st)
-                      : launch_gemm<xmc::UpdPolicy<true, false>>(map_g_k, map_xt, up, u_tiles, h->sm_count, st);
-      else rc = sr ? launch_gemm<xmc::UpdPolicy<false, true>>(map_g_k, map_xt, up, u_tiles, h->sm_count, st)
-                   : launch_gemm<xmc::UpdPolicy<false, false>>(map_g_k, map_xt, up, u_tiles, h->sm_count, st);
+      // the reference pairs: e4m3 weights (no dW rounding), bf16 weights (dW materialised in bf16);
+      // weight decay is off in both, so only those combinations get the branch-free fast kernels
+      const bool rdw = up.round_dw_bf16 != 0, has_wd = wd != 0.f;
+#define XMC_UPD(W8_, SR_, RD_, WD_) \
+  launch_gemm<xmc::UpdPolicy<W8_, SR_, RD_, WD_>>(map_g_k, map_xt, up, u_tiles, h->sm_count, st)
+      if (w8) {
+        if (!rdw && !has_wd) rc = sr ? XMC_UPD(true, true, false, false) : XMC_UPD(true, false, false, false);
+        else if (!rdw) rc = sr ? XMC_UPD(true, true, false, true) : XMC_UPD(true, false, false, true);
+        else rc = sr ? XMC_UPD(true, true, true, true) : XMC_UPD(true, false, true, true);
+      } else {
+        if (rdw && !has_wd) rc = sr ? XMC_UPD(false, true, true, false) : XMC_UPD(false, false, true, false);
+        else if (rdw) rc = sr ? XMC_UPD(false, true, true, true) : XMC_UPD(false, false, true, true);
+        else rc = sr ? XMC_UPD(false, true, false, true) : XMC_UPD(false, false, false, true);
+      }
+#undef XMC_UPD
       if (rc) return rc;
       first = false;
       ++launch_idx;
@@ -504,7 +515,7 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
   }
   if (want_loss) {
     mark(h, K_REDUCE, st);
-    xmc::reduce_loss_kernel<<<1, 32, 0, st>>>(h->loss_partial, launch_idx * h->sm_count * 4, loss_out);
+    xmc::reduce_loss_kernel<<<1, 32, 0, st>>>(h->loss_partial, launch_idx * h->sm_count * xmc::kMaxEpiWarps, loss_out);
     CU_TRY(cudaGetLastError());
   }
   mark(h, K_END, st);

@@ -40,6 +40,7 @@ struct FwdPolicy {
   static constexpr bool kFp8 = FP8;
   static constexpr uint32_t kFmt = FP8 ? 0u : 1u;            // e4m3 | bf16
   static constexpr int kElemsPerRow = FP8 ? 128 : 64;
+  static constexpr int kEpiWarps = 8;
   struct EpilogueState {
     float loss;
     int has_pos;
@@ -60,30 +61,33 @@ struct FwdPolicy {
     st.has_pos = 0;
   }
   // Build this warp's 32 rows of the positives bitmap (duplicates collapse: set semantics).
-  __device__ static void epilogue_pre(const Params& p, const Job& j, SharedTail& sh, int q, int lane,
+  // Each warp owns the bitmap words of its rows (quarter q) and of its column groups (phase h).
+  __device__ static void epilogue_pre(const Params& p, const Job& j, SharedTail& sh, const EpiCtx& ec,
                                       EpilogueState& st) {
     const int beg = p.bucket_off[p.tile_base + j.t0], end = p.bucket_off[p.tile_base + j.t0 + 1];
     st.has_pos = end > beg;
     if (!st.has_pos) return;
-    uint32_t* bm = sh.bitmap + q * 32 * (kTileN / 32);
+    constexpr int kWordsPerRow = kTileN / 32;
     __syncwarp();
-    for (int w = lane; w < 32 * (kTileN / 32); w += 32) bm[w] = 0u;
+    for (int w = ec.lane; w < 32 * kWordsPerRow; w += 32) {
+      if ((w % kWordsPerRow) % ec.nsplit == ec.h) sh.bitmap[ec.q * 32 * kWordsPerRow + w] = 0u;
+    }
     __syncwarp();
-    for (int e = beg + lane; e < end; e += 32) {
+    for (int e = beg + ec.lane; e < end; e += 32) {
       const uint32_t ent = p.bucket_ent[e];
       const int lrow = (int)(ent >> 16), bl = (int)(ent & 0xFFFFu) - j.b0;
-      if ((lrow >> 5) == q && bl >= 0 && bl < kTileN)
-        atomicOr(&sh.bitmap[lrow * (kTileN / 32) + (bl >> 5)], 1u << (bl & 31));
+      if ((lrow >> 5) == ec.q && bl >= 0 && bl < kTileN && ((bl >> 5) % ec.nsplit) == ec.h)
+        atomicOr(&sh.bitmap[lrow * kWordsPerRow + (bl >> 5)], 1u << (bl & 31));
     }
     __syncwarp();
   }
   __device__ static void epilogue(const Params& p, const Job& j, uint32_t taddr, bool have_acc,
-                                  SharedTail& sh, int q, int lane, EpilogueState& st) {
-    const int row = q * 32 + lane;
+                                  SharedTail& sh, const EpiCtx& ec, EpilogueState& st) {
+    const int row = ec.q * 32 + ec.lane;
     const int crow = j.a0 + row;
     const bool row_valid = crow < p.rows_valid;
     __nv_bfloat16* grow = p.G + (size_t)crow * p.bpad + j.b0;
-    for (int c0 = 0; c0 < j.n_eff; c0 += 32) {
+    for (int c0 = 32 * ec.h; c0 < j.n_eff; c0 += 32 * ec.nsplit) {
       uint32_t v[32];
       if (have_acc) {
         tmem_ld32(taddr + c0, v);
@@ -94,21 +98,50 @@ struct FwdPolicy {
       }
       const uint32_t bits = st.has_pos ? sh.bitmap[row * (kTileN / 32) + (c0 >> 5)] : 0u;
       uint32_t out[16];
+      // Per pair: one packed cvt rounds the logits to bf16, ex2 + rcp give the sigmoid, one packed cvt
+      // rounds and packs it.  (cvt shares the special-function pipe with ex2/rcp; integer rounding
+      // would move the bottleneck to the ALU pipe instead.)
 #pragma unroll
       for (int i = 0; i < 32; i += 2) {
-        float g[2];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int b = j.b0 + c0 + i + h;
-          const bool pos = (bits >> (i + h)) & 1u;
-          const float z = bf16_round(__uint_as_float(v[i + h]) * p.w_scale);
-          float s = sigmoid_bf16(z);
-          if (pos) s = bf16_round(s - 1.0f);
-          const bool ok = row_valid && b < p.batch;
-          if (LOSS && ok) st.loss += bce_softplus(z) - (pos ? z : 0.f);
-          g[h] = ok ? s : 0.f;
+        const uint32_t zz = pack_bf16x2(__uint_as_float(v[i]) * p.w_scale, __uint_as_float(v[i + 1]) * p.w_scale);
+        const float z0 = __uint_as_float(zz << 16), z1 = __uint_as_float(zz & 0xFFFF0000u);
+        const float s0 = fast_sigmoid(z0), s1 = fast_sigmoid(z1);
+        out[i >> 1] = pack_bf16x2(s0, s1);
+        if (LOSS) {
+          if (row_valid && j.b0 + c0 + i < p.batch) st.loss += bce_softplus(z0);
+          if (row_valid && j.b0 + c0 + i + 1 < p.batch) st.loss += bce_softplus(z1);
         }
-        out[i >> 1] = pack_bf16x2(g[0], g[1]);
+      }
+      // positives: G = bf16(sigmoid) - 1 in bf16 arithmetic.  Rare (a few thousand pairs per step), so
+      // only threads that own one take this path; indices stay compile-time to keep out[] in registers.
+      if (bits != 0u) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const uint32_t two = (bits >> (2 * i)) & 3u;
+          if (two == 0u) continue;
+          const uint32_t word = out[i];
+          float lo = __uint_as_float(word << 16), hi = __uint_as_float(word & 0xFFFF0000u);
+          if (two & 1u) lo = bf16_round(lo - 1.0f);
+          if (two & 2u) hi = bf16_round(hi - 1.0f);
+          out[i] = __byte_perm(__float_as_uint(lo), __float_as_uint(hi), 0x7632);
+          if (LOSS && row_valid) {
+            // loss term -y*z: z recomputed from the accumulator with the same rounding
+            if ((two & 1u) && j.b0 + c0 + 2 * i < p.batch) st.loss -= bf16_round(__uint_as_float(v[2 * i]) * p.w_scale);
+            if ((two & 2u) && j.b0 + c0 + 2 * i + 1 < p.batch) st.loss -= bf16_round(__uint_as_float(v[2 * i + 1]) * p.w_scale);
+          }
+        }
+      }
+      // rows beyond the chunk and batch columns beyond the batch carry G = 0
+      if (!row_valid) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) out[i] = 0u;
+      } else if (j.b0 + c0 + 32 > p.batch) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int b = j.b0 + c0 + 2 * i;
+          if (b >= p.batch) out[i] = 0u;
+          else if (b + 1 >= p.batch) out[i] &= 0x0000FFFFu;
+        }
       }
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -118,12 +151,12 @@ struct FwdPolicy {
       }
     }
   }
-  __device__ static void epilogue_end(const Params& p, SharedTail&, int q, int lane, EpilogueState& st) {
+  __device__ static void epilogue_end(const Params& p, SharedTail&, const EpiCtx& ec, EpilogueState& st) {
     if (!LOSS) return;
     float v = st.loss;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    if (lane == 0 && p.loss_partial != nullptr) p.loss_partial[blockIdx.x * 4 + q] = (double)v;
+    if (ec.lane == 0 && p.loss_partial != nullptr) p.loss_partial[blockIdx.x * kMaxEpiWarps + ec.slot] = (double)v;
   }
 };
 
@@ -145,14 +178,18 @@ struct UpdParams {
   int* status;
 };
 
-template <bool W8, bool SR>
+template <bool W8, bool SR, bool ROUND_DW, bool HAS_WD>
 struct UpdPolicy {
   using Params = UpdParams;
   static constexpr bool kMnMajor = false;
   static constexpr bool kFp8 = false;
   static constexpr uint32_t kFmt = 1u;
   static constexpr int kElemsPerRow = 64;
-  using EpilogueState = NoState;
+  static constexpr int kEpiWarps = 8;
+  static constexpr int kGroups = (kTileN / 32) / (kEpiWarps / 4);   // 32-column groups per thread and tile
+  struct EpilogueState {
+    uint4 wpre[W8 ? 2 * kGroups : 1];     // this thread's e4m3 weights of the tile, fetched ahead
+  };
 
   __device__ static int num_tiles(const Params& p) { return p.n_ltiles * p.n_dtiles; }
   __device__ static void job(const Params& p, int tile, Job& j) {
@@ -165,98 +202,150 @@ struct UpdPolicy {
     j.n_eff = min(kTileN, round_up16(p.d - j.b0));
   }
   __device__ static void epilogue_begin(const Params&, EpilogueState&) {}
-  __device__ static void epilogue_pre(const Params&, const Job&, SharedTail&, int, int, EpilogueState&) {}
-  __device__ static void epilogue_end(const Params&, SharedTail&, int, int, EpilogueState&) {}
+  __device__ static void epilogue_end(const Params&, SharedTail&, const EpiCtx&, EpilogueState&) {}
 
-  // new weights for 8 consecutive elements
-  __device__ static void update8(const Params& p, const float (&w)[8], const uint32_t* acc,
-                                 unsigned long long elem, float (&o)[8], uint32_t (&r16)[8]) {
-    if (SR) {
-      const unsigned long long qi = elem >> 3;
-      const uint4 r = philox4x32_10(
-          make_uint4((uint32_t)qi, (uint32_t)(qi >> 32), (uint32_t)p.step, (uint32_t)(p.step >> 32)),
-          make_uint2((uint32_t)p.seed, (uint32_t)(p.seed >> 32)));
-      r16[0] = r.x & 0xFFFFu; r16[1] = r.x >> 16; r16[2] = r.y & 0xFFFFu; r16[3] = r.y >> 16;
-      r16[4] = r.z & 0xFFFFu; r16[5] = r.z >> 16; r16[6] = r.w & 0xFFFFu; r16[7] = r.w >> 16;
+  // Fetch the tile's weights while its MMAs are still running.
+  __device__ static void epilogue_pre(const Params& p, const Job& j, SharedTail&, const EpiCtx& ec,
+                                      EpilogueState& st) {
+    if constexpr (W8) {
+      const int crow = j.a0 + ec.q * 32 + ec.lane;
+      const bool row_valid = crow < p.rows_valid;
+      const uint8_t* wrow = reinterpret_cast<const uint8_t*>(p.W) + (size_t)crow * p.d + j.b0;
+#pragma unroll
+      for (int g = 0; g < kGroups; ++g) {
+        const int c0 = 32 * (ec.h + ec.nsplit * g);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const bool ok = row_valid && c0 < j.n_eff && j.b0 + c0 + 16 * h < p.d;
+          st.wpre[2 * g + h] = ok ? *reinterpret_cast<const uint4*>(wrow + c0 + 16 * h) : make_uint4(0, 0, 0, 0);
+        }
+      }
+    }
+  }
+
+  // 16 random bits for each of 32 consecutive elements starting at `elem` (multiple of 8): four
+  // Philox calls advanced round by round together so that their multiply chains overlap.
+  __device__ static void random32(const Params& p, unsigned long long elem, uint32_t (&r)[16]) {
+    constexpr uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
+    uint4 c[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const unsigned long long qi = (elem >> 3) + i;
+      c[i] = make_uint4((uint32_t)qi, (uint32_t)(qi >> 32), (uint32_t)p.step, (uint32_t)(p.step >> 32));
+    }
+    uint32_t k0 = (uint32_t)p.seed, k1 = (uint32_t)(p.seed >> 32);
+#pragma unroll
+    for (int rd = 0; rd < 10; ++rd) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t hi0 = __umulhi(M0, c[i].x), lo0 = M0 * c[i].x;
+        const uint32_t hi1 = __umulhi(M1, c[i].z), lo1 = M1 * c[i].z;
+        c[i] = make_uint4(hi1 ^ c[i].y ^ k0, lo1, hi0 ^ c[i].w ^ k1, lo0);
+      }
+      k0 += W0;
+      k1 += W1;
     }
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      float a = __uint_as_float(acc[i]);
-      if (p.round_dw_bf16) a = bf16_round(a);
-      if (p.wd != 0.f) a = fmaf(p.wd, w[i], a);
-      o[i] = fmaf(-p.lr_eff, a, w[i]);
+    for (int i = 0; i < 4; ++i) {
+      r[4 * i] = c[i].x; r[4 * i + 1] = c[i].y; r[4 * i + 2] = c[i].z; r[4 * i + 3] = c[i].w;
+    }
+  }
+  // element e (0..31) of the group takes half (e & 1) of word e >> 1
+  __device__ static uint32_t r16_of(const uint32_t (&r)[16], int e) {
+    return (e & 1) ? (r[e >> 1] >> 16) : (r[e >> 1] & 0xFFFFu);
+  }
+  __device__ static float new_weight(const Params& p, float w, uint32_t acc_bits) {
+    // no run-time branches in here: they would cut the per-element code into tiny basic blocks
+    float a = __uint_as_float(acc_bits);
+    if constexpr (ROUND_DW) a = bf16_round(a);
+    if constexpr (HAS_WD) a = fmaf(p.wd, w, a);
+    return fmaf(-p.lr_eff, a, w);
+  }
+
+  // one 32-column group of one row: v = accumulators, w16[2] = the row's 32 e4m3 weights
+  __device__ static void process_w8(const Params& p, const uint32_t (&v)[32], const uint4 (&w16)[2],
+                                    unsigned long long elem, uint8_t* dst, bool store_lo, bool store_hi) {
+    uint32_t r[16];
+    if (SR) random32(p, elem, r);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t rw[4] = {w16[h].x, w16[h].y, w16[h].z, w16[h].w};
+      uint32_t ow[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {          // 4 elements per 32-bit word
+        float o[4];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const float2 f = e4m3x2_to_float2((uint16_t)(rw[k] >> (16 * i)));
+          const int e = 16 * h + 4 * k + 2 * i;
+          o[2 * i] = new_weight(p, f.x, v[e]);
+          o[2 * i + 1] = new_weight(p, f.y, v[e + 1]);
+          if (SR) {
+            o[2 * i] = sr_e4m3(o[2 * i], r16_of(r, e));
+            o[2 * i + 1] = sr_e4m3(o[2 * i + 1], r16_of(r, e + 1));
+          }
+        }
+        ow[k] = (uint32_t)float2_to_e4m3x2(o[0], o[1]) | ((uint32_t)float2_to_e4m3x2(o[2], o[3]) << 16);
+      }
+      if (h == 0 ? store_lo : store_hi)
+        *reinterpret_cast<uint4*>(dst + 16 * h) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+  }
+
+  __device__ static void process_bf16(const Params& p, const uint32_t (&v)[32], unsigned long long elem,
+                                      __nv_bfloat16* wp, int valid16) {
+    uint32_t r[16];
+    if (SR) random32(p, elem, r);
+#pragma unroll
+    for (int g8 = 0; g8 < 4; ++g8) {
+      if (g8 >= 2 * valid16) break;
+      const uint4 raw = *reinterpret_cast<const uint4*>(wp + 8 * g8);
+      const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
+      uint32_t ow[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int e = 8 * g8 + 2 * i;
+        const float o0 = new_weight(p, bf16_bits_to_float(rw[i] & 0xFFFFu), v[e]);
+        const float o1 = new_weight(p, bf16_bits_to_float(rw[i] >> 16), v[e + 1]);
+        if (SR) ow[i] = sr_bf16_bits(o0, r16_of(r, e)) | (sr_bf16_bits(o1, r16_of(r, e + 1)) << 16);
+        else ow[i] = pack_bf16x2(o0, o1);
+      }
+      *reinterpret_cast<uint4*>(wp + 8 * g8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
     }
   }
 
   __device__ static void epilogue(const Params& p, const Job& j, uint32_t taddr, bool have_acc,
-                                  SharedTail&, int q, int lane, EpilogueState&) {
-    const int row = q * 32 + lane;
+                                  SharedTail&, const EpiCtx& ec, EpilogueState& st) {
+    const int row = ec.q * 32 + ec.lane;
     const int crow = j.a0 + row;
     const bool row_valid = crow < p.rows_valid;
-    for (int c0 = 0; c0 < j.n_eff; c0 += 32) {
-      uint32_t v[32];
+    const unsigned long long erow = p.elem0 + (unsigned long long)crow * p.d + j.b0;
+    uint32_t va[32], vb[32];
+    // TMEM loads run one group ahead of the arithmetic
+    if (have_acc && 32 * ec.h < j.n_eff) tmem_ld32(taddr + 32 * ec.h, va);
+#pragma unroll
+    for (int g = 0; g < kGroups; ++g) {
+      const int c0 = 32 * (ec.h + ec.nsplit * g);
+      if (c0 >= j.n_eff) break;
+      uint32_t (&cur)[32] = (g & 1) ? vb : va;
+      uint32_t (&nxt)[32] = (g & 1) ? va : vb;
       if (have_acc) {
-        tmem_ld32(taddr + c0, v);
         tmem_ld_wait();
+        const int c1 = c0 + 32 * ec.nsplit;
+        if (g + 1 < kGroups && c1 < j.n_eff) tmem_ld32(taddr + c1, nxt);
       } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = 0u;
+        for (int i = 0; i < 32; ++i) cur[i] = 0u;
       }
       if (!row_valid) continue;
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int col = j.b0 + c0 + 16 * h;
-        if (col >= p.d) continue;
-        const unsigned long long e0 = p.elem0 + (unsigned long long)crow * p.d + col;
-        if constexpr (W8) {
-          uint8_t* wp = reinterpret_cast<uint8_t*>(p.W) + (size_t)crow * p.d + col;
-          const uint4 raw = *reinterpret_cast<const uint4*>(wp);
-          const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
-          uint32_t ow[4];
-#pragma unroll
-          for (int g8 = 0; g8 < 2; ++g8) {
-            float w[8], o[8];
-            uint32_t r16[8];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float2 f = e4m3x2_to_float2((uint16_t)(rw[2 * g8 + (i >> 1)] >> (16 * (i & 1))));
-              w[2 * i] = f.x;
-              w[2 * i + 1] = f.y;
-            }
-            update8(p, w, &v[16 * h + 8 * g8], e0 + 8 * g8, o, r16);
-            if (SR) {
-#pragma unroll
-              for (int i = 0; i < 8; ++i) o[i] = sr_e4m3(o[i], r16[i]);
-            }
-#pragma unroll
-            for (int i = 0; i < 2; ++i)
-              ow[2 * g8 + i] = (uint32_t)float2_to_e4m3x2(o[4 * i], o[4 * i + 1]) |
-                               ((uint32_t)float2_to_e4m3x2(o[4 * i + 2], o[4 * i + 3]) << 16);
-          }
-          *reinterpret_cast<uint4*>(wp) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
-        } else {
-          __nv_bfloat16* wp = reinterpret_cast<__nv_bfloat16*>(p.W) + (size_t)crow * p.d + col;
-#pragma unroll
-          for (int g8 = 0; g8 < 2; ++g8) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(wp + 8 * g8);
-            const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
-            float w[8], o[8];
-            uint32_t r16[8];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              w[2 * i] = bf16_bits_to_float(rw[i] & 0xFFFFu);
-              w[2 * i + 1] = bf16_bits_to_float(rw[i] >> 16);
-            }
-            update8(p, w, &v[16 * h + 8 * g8], e0 + 8 * g8, o, r16);
-            uint32_t ow[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              if (SR) ow[i] = sr_bf16_bits(o[2 * i], r16[2 * i]) | (sr_bf16_bits(o[2 * i + 1], r16[2 * i + 1]) << 16);
-              else ow[i] = pack_bf16x2(o[2 * i], o[2 * i + 1]);
-            }
-            *reinterpret_cast<uint4*>(wp + 8 * g8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
-          }
-        }
+      const int col = j.b0 + c0;
+      if constexpr (W8) {
+        uint8_t* wp = reinterpret_cast<uint8_t*>(p.W) + (size_t)crow * p.d + col;
+        const uint4 w16[2] = {st.wpre[2 * g], st.wpre[2 * g + 1]};
+        process_w8(p, cur, w16, erow + c0, wp, col < p.d, col + 16 < p.d);
+      } else {
+        __nv_bfloat16* wp = reinterpret_cast<__nv_bfloat16*>(p.W) + (size_t)crow * p.d + col;
+        process_bf16(p, cur, erow + c0, wp, col + 16 < p.d ? 2 : (col < p.d ? 1 : 0));
       }
     }
   }
@@ -282,6 +371,7 @@ struct GradXPolicy {
   static constexpr bool kFp8 = false;
   static constexpr uint32_t kFmt = 1u;
   static constexpr int kElemsPerRow = 64;
+  static constexpr int kEpiWarps = 4;
   using EpilogueState = NoState;
 
   __device__ static int num_tiles(const Params& p) { return p.n_btiles * p.n_dtiles * p.n_splits; }
@@ -298,15 +388,15 @@ struct GradXPolicy {
     j.n_eff = min(kTileN, round_up16(p.d - j.b0));
   }
   __device__ static void epilogue_begin(const Params&, EpilogueState&) {}
-  __device__ static void epilogue_pre(const Params&, const Job&, SharedTail&, int, int, EpilogueState&) {}
-  __device__ static void epilogue_end(const Params&, SharedTail&, int, int, EpilogueState&) {}
+  __device__ static void epilogue_pre(const Params&, const Job&, SharedTail&, const EpiCtx&, EpilogueState&) {}
+  __device__ static void epilogue_end(const Params&, SharedTail&, const EpiCtx&, EpilogueState&) {}
   __device__ static void epilogue(const Params& p, const Job& j, uint32_t taddr, bool have_acc,
-                                  SharedTail&, int q, int lane, EpilogueState&) {
-    const int b = j.a0 + q * 32 + lane;
+                                  SharedTail&, const EpiCtx& ec, EpilogueState&) {
+    const int b = j.a0 + ec.q * 32 + ec.lane;
     const bool row_valid = b < p.bpad;
     if (!have_acc && p.accumulate) return;
     float* dst = p.partial + ((size_t)j.t2 * p.bpad + b) * p.d + j.b0;
-    for (int c0 = 0; c0 < j.n_eff; c0 += 32) {
+    for (int c0 = 32 * ec.h; c0 < j.n_eff; c0 += 32 * ec.nsplit) {
       uint32_t v[32];
       if (have_acc) {
         tmem_ld32(taddr + c0, v);
@@ -351,6 +441,7 @@ struct PlainPolicy {
   static constexpr bool kFp8 = FP8;
   static constexpr uint32_t kFmt = FP8 ? 0u : 1u;
   static constexpr int kElemsPerRow = FP8 ? 128 : 64;
+  static constexpr int kEpiWarps = 8;
   using EpilogueState = NoState;
   __device__ static int num_tiles(const Params& p) { return p.n_mtiles * p.n_ntiles; }
   __device__ static void job(const Params& p, int tile, Job& j) {
@@ -363,12 +454,12 @@ struct PlainPolicy {
     j.n_eff = min(kTileN, round_up16(p.N - j.b0));
   }
   __device__ static void epilogue_begin(const Params&, EpilogueState&) {}
-  __device__ static void epilogue_pre(const Params&, const Job&, SharedTail&, int, int, EpilogueState&) {}
-  __device__ static void epilogue_end(const Params&, SharedTail&, int, int, EpilogueState&) {}
+  __device__ static void epilogue_pre(const Params&, const Job&, SharedTail&, const EpiCtx&, EpilogueState&) {}
+  __device__ static void epilogue_end(const Params&, SharedTail&, const EpiCtx&, EpilogueState&) {}
   __device__ static void epilogue(const Params& p, const Job& j, uint32_t taddr, bool have_acc,
-                                  SharedTail&, int q, int lane, EpilogueState&) {
-    const int m = j.a0 + q * 32 + lane;
-    for (int c0 = 0; c0 < j.n_eff; c0 += 32) {
+                                  SharedTail&, const EpiCtx& ec, EpilogueState&) {
+    const int m = j.a0 + ec.q * 32 + ec.lane;
+    for (int c0 = 32 * ec.h; c0 < j.n_eff; c0 += 32 * ec.nsplit) {
       uint32_t v[32];
       if (have_acc) {
         tmem_ld32(taddr + c0, v);
