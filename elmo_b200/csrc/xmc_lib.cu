@@ -232,9 +232,10 @@ int xmc_create(const xmc_config* cfg, xmc_handle** out) {
   if (cfg->sched_labels > 0) {
     h->sched = (int)cfg->sched_labels;
   } else {
-    // keep one chunk of G (sched x bpad bf16) near 32 MB so it stays in L2 between its three consumers
-    long long s = (32ll << 20) / ((long long)h->bpad_max * 2);
-    s = std::max(1024ll, std::min(s, 131072ll));
+    // Labels per scheduling chunk: as many as the reference chunk allows (fewer, longer launches
+    // amortise the per-launch ramp), bounded so that one chunk of G (sched x bpad bf16) stays <= 128 MB.
+    long long s = (128ll << 20) / ((long long)h->bpad_max * 2);
+    s = std::max(1024ll, std::min(s, 65536ll));
     h->sched = (int)(s / 128 * 128);
   }
   const int d = cfg->dim;

@@ -40,7 +40,10 @@ struct FwdPolicy {
   static constexpr bool kFp8 = FP8;
   static constexpr uint32_t kFmt = FP8 ? 0u : 1u;            // e4m3 | bf16
   static constexpr int kElemsPerRow = FP8 ? 128 : 64;
-  static constexpr int kEpiWarps = 8;
+#ifndef XMC_FWD_WARPS
+#define XMC_FWD_WARPS 8
+#endif
+  static constexpr int kEpiWarps = XMC_FWD_WARPS;
   struct EpilogueState {
     float loss;
     int has_pos;
@@ -185,11 +188,12 @@ struct UpdPolicy {
   static constexpr bool kFp8 = false;
   static constexpr uint32_t kFmt = 1u;
   static constexpr int kElemsPerRow = 64;
-  static constexpr int kEpiWarps = 8;
-  static constexpr int kGroups = (kTileN / 32) / (kEpiWarps / 4);   // 32-column groups per thread and tile
-  struct EpilogueState {
-    uint4 wpre[W8 ? 2 * kGroups : 1];     // this thread's e4m3 weights of the tile, fetched ahead
-  };
+#ifndef XMC_UPD_WARPS
+#define XMC_UPD_WARPS 16
+#endif
+  static constexpr int kEpiWarps = XMC_UPD_WARPS;
+  static constexpr int kGroups = ((kTileN / 32) + (kEpiWarps / 4) - 1) / (kEpiWarps / 4);   // 32-column groups per thread and tile
+  using EpilogueState = NoState;
 
   __device__ static int num_tiles(const Params& p) { return p.n_ltiles * p.n_dtiles; }
   __device__ static void job(const Params& p, int tile, Job& j) {
@@ -204,22 +208,14 @@ struct UpdPolicy {
   __device__ static void epilogue_begin(const Params&, EpilogueState&) {}
   __device__ static void epilogue_end(const Params&, SharedTail&, const EpiCtx&, EpilogueState&) {}
 
-  // Fetch the tile's weights while its MMAs are still running.
-  __device__ static void epilogue_pre(const Params& p, const Job& j, SharedTail&, const EpiCtx& ec,
-                                      EpilogueState& st) {
-    if constexpr (W8) {
-      const int crow = j.a0 + ec.q * 32 + ec.lane;
-      const bool row_valid = crow < p.rows_valid;
-      const uint8_t* wrow = reinterpret_cast<const uint8_t*>(p.W) + (size_t)crow * p.d + j.b0;
+  __device__ static void epilogue_pre(const Params&, const Job&, SharedTail&, const EpiCtx&, EpilogueState&) {}
+  __device__ static void load_acc(uint32_t taddr, bool have_acc, uint32_t (&v)[32]) {
+    if (have_acc) {
+      tmem_ld32(taddr, v);
+      tmem_ld_wait();
+    } else {
 #pragma unroll
-      for (int g = 0; g < kGroups; ++g) {
-        const int c0 = 32 * (ec.h + ec.nsplit * g);
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const bool ok = row_valid && c0 < j.n_eff && j.b0 + c0 + 16 * h < p.d;
-          st.wpre[2 * g + h] = ok ? *reinterpret_cast<const uint4*>(wrow + c0 + 16 * h) : make_uint4(0, 0, 0, 0);
-        }
-      }
+      for (int i = 0; i < 32; ++i) v[i] = 0u;
     }
   }
 
@@ -238,9 +234,11 @@ struct UpdPolicy {
     for (int rd = 0; rd < 10; ++rd) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const uint32_t hi0 = __umulhi(M0, c[i].x), lo0 = M0 * c[i].x;
-        const uint32_t hi1 = __umulhi(M1, c[i].z), lo1 = M1 * c[i].z;
-        c[i] = make_uint4(hi1 ^ c[i].y ^ k0, lo1, hi0 ^ c[i].w ^ k1, lo0);
+        // one widening multiply yields both halves
+        const unsigned long long p0 = (unsigned long long)M0 * c[i].x;
+        const unsigned long long p1 = (unsigned long long)M1 * c[i].z;
+        c[i] = make_uint4((uint32_t)(p1 >> 32) ^ c[i].y ^ k0, (uint32_t)p1, (uint32_t)(p0 >> 32) ^ c[i].w ^ k1,
+                          (uint32_t)p0);
       }
       k0 += W0;
       k1 += W1;
@@ -320,32 +318,27 @@ struct UpdPolicy {
     const int crow = j.a0 + row;
     const bool row_valid = crow < p.rows_valid;
     const unsigned long long erow = p.elem0 + (unsigned long long)crow * p.d + j.b0;
-    uint32_t va[32], vb[32];
-    // TMEM loads run one group ahead of the arithmetic
-    if (have_acc && 32 * ec.h < j.n_eff) tmem_ld32(taddr + 32 * ec.h, va);
-#pragma unroll
+    // One group body in the instruction stream (the unrolled form overflowed the instruction cache and
+    // the register file); latency is hidden by running 16 epilogue warps instead.
+    uint32_t v[32];
+#pragma unroll 1
     for (int g = 0; g < kGroups; ++g) {
       const int c0 = 32 * (ec.h + ec.nsplit * g);
       if (c0 >= j.n_eff) break;
-      uint32_t (&cur)[32] = (g & 1) ? vb : va;
-      uint32_t (&nxt)[32] = (g & 1) ? va : vb;
-      if (have_acc) {
-        tmem_ld_wait();
-        const int c1 = c0 + 32 * ec.nsplit;
-        if (g + 1 < kGroups && c1 < j.n_eff) tmem_ld32(taddr + c1, nxt);
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) cur[i] = 0u;
-      }
-      if (!row_valid) continue;
       const int col = j.b0 + c0;
       if constexpr (W8) {
         uint8_t* wp = reinterpret_cast<uint8_t*>(p.W) + (size_t)crow * p.d + col;
-        const uint4 w16[2] = {st.wpre[2 * g], st.wpre[2 * g + 1]};
-        process_w8(p, cur, w16, erow + c0, wp, col < p.d, col + 16 < p.d);
+        uint4 w16[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          w16[h] = (row_valid && col + 16 * h < p.d) ? *reinterpret_cast<const uint4*>(wp + 16 * h)
+                                                     : make_uint4(0, 0, 0, 0);
+        load_acc(taddr + c0, have_acc, v);
+        if (row_valid) process_w8(p, v, w16, erow + c0, wp, col < p.d, col + 16 < p.d);
       } else {
         __nv_bfloat16* wp = reinterpret_cast<__nv_bfloat16*>(p.W) + (size_t)crow * p.d + col;
-        process_bf16(p, cur, erow + c0, wp, col + 16 < p.d ? 2 : (col < p.d ? 1 : 0));
+        load_acc(taddr + c0, have_acc, v);
+        if (row_valid) process_bf16(p, v, erow + c0, wp, col + 16 < p.d ? 2 : (col < p.d ? 1 : 0));
       }
     }
   }
