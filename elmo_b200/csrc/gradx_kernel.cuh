@@ -1,0 +1,252 @@
+// grad_X partial sums: partial[split][b][c] (+)= sum over a slice of the chunk's label rows of
+// G[l][b] * W[l][c]   (reference: matmul_kernel.py:204-239 large_k_matmul, C = G^T W, operands
+// rounded to bf16, fp32 accumulation).
+//
+// One CTA owns a 256 (batch) x 256 (feature) output tile for one slice of label rows: two 128-lane
+// TMEM accumulators of 256 columns.  Both operands are "MN-major" for the tensor core (the
+// contraction index, the label row, is the slow index of G[l][b] and W[l][c]), so G tiles land by
+// TMA exactly as stored.  e4m3 weights are brought in raw (half the L2 traffic of a bf16 copy and
+// no staging pass over HBM) and turned into the bf16 128-byte-swizzled operand layout by the eight
+// epilogue warps while the previous stage is being multiplied; after the last stage the same warps
+// drain the accumulators.  Each (split, tile) owns its slot of `partial` and adds to it in chunk
+// order: fixed summation order, no atomics.
+#pragma once
+#include "gemm_engine.cuh"
+#include "numerics.cuh"
+
+namespace xmc {
+
+constexpr int kGxRows = 32;                           // label rows per pipeline stage
+constexpr int kGxStages = 5;
+constexpr int kGxRawStages = 6;
+constexpr int kGxABytes = 4 * kGxRows * 128;          // 4 blocks of 64 batch columns: 16 KB
+constexpr int kGxBBytes = 4 * kGxRows * 128;          // 4 blocks of 64 features, bf16: 16 KB
+constexpr int kGxRawBytes = kGxRows * 256;            // raw e4m3 tile: 8 KB
+constexpr int kGxBlockBytes = kGxRows * 128;          // one 64-element block of a stage: 4 KB
+constexpr int kGxWarps = 8;
+constexpr int kGxThreads = 64 + 32 * kGxWarps;
+
+struct GxParams {
+  int bpad, d;
+  int n_btiles, n_dtiles, n_splits;   // batch tiles of 256, feature tiles of 256
+  int total_ksteps;                   // cdiv(label rows written by the forward kernel, 32)
+  int accumulate;                     // 0: overwrite the slot (first chunk of a step)
+  float* partial;                     // [n_splits][bpad][d]
+  int* status;
+};
+
+struct GxShared {
+  uint64_t a_full[kGxStages];
+  uint64_t b_full[kGxStages];         // converted (or TMA-loaded) weight block ready
+  uint64_t mma_done[kGxStages];       // the MMAs reading stage s have completed
+  uint64_t raw_full[kGxRawStages];
+  uint64_t raw_empty[kGxRawStages];
+  uint64_t tmem_full;
+  uint32_t tmem_base;
+  Ctl ctl;
+};
+
+constexpr int kGxSmemBytes = kGxStages * (kGxABytes + kGxBBytes) + kGxRawStages * kGxRawBytes +
+                             (int)sizeof(GxShared) + 1024;
+
+// four e4m3 bytes -> four bf16 (two packed words), exact, integer/FMA pipes only.
+// (b & 0x7f) << 4 placed in a bf16 is the value times 2^-120, subnormals included; one packed
+// multiply by 2^120 restores it.
+__device__ __forceinline__ void e4m3x4_to_bf16x4(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  const uint32_t t0 = __byte_perm(w, 0u, 0x1404);     // b1 << 24 | b0 << 8
+  const uint32_t t1 = __byte_perm(w, 0u, 0x3424);     // b3 << 24 | b2 << 8
+  const uint32_t x0 = (t0 & 0x80008000u) | ((t0 >> 4) & 0x07F007F0u);
+  const uint32_t x1 = (t1 & 0x80008000u) | ((t1 >> 4) & 0x07F007F0u);
+  const uint32_t scale = 0x7B807B80u;                 // bf16x2 (2^120, 2^120)
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(lo) : "r"(x0), "r"(scale));
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(hi) : "r"(x1), "r"(scale));
+}
+
+template <bool CONVERT>
+__global__ void __launch_bounds__(kGxThreads, 1)
+gradx_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant__ CUtensorMap map_w,
+             const GxParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* smem_a = smem;                                         // [stage][4 blocks][32 rows][128 B]
+  uint8_t* smem_b = smem + kGxStages * kGxABytes;                 // same shape, bf16 weights
+  uint8_t* smem_r = smem_b + kGxStages * kGxBBytes;               // [raw stage][32 rows][256 B] e4m3
+  GxShared& sh = *reinterpret_cast<GxShared*>(smem_r + kGxRawStages * kGxRawBytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  static_assert(kGxWarps == 8 && kGxRows == 32, "converter mapping assumes 8 warps x 32 rows");
+
+  // tile coordinates
+  const int per = p.n_btiles * p.n_dtiles;
+  const int split = blockIdx.x / per;
+  const int rem = blockIdx.x - split * per;
+  const int bt = rem / p.n_dtiles, dt = rem - bt * p.n_dtiles;
+  const int b0 = bt * 256, c0 = dt * 256;
+  const int k_begin = (int)(((long long)split * p.total_ksteps) / p.n_splits);
+  const int k_steps = (int)(((long long)(split + 1) * p.total_ksteps) / p.n_splits) - k_begin;
+  const int n_eff = min(256, (p.d - c0 + 15) & ~15);
+  const int m_halves = (b0 + 128 < p.bpad) ? 2 : 1;               // accumulators in use
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kGxStages; ++s) {
+      mbar_init(smem_u32(&sh.a_full[s]), 1);
+      mbar_init(smem_u32(&sh.b_full[s]), CONVERT ? 32 * kGxWarps : 1);
+      mbar_init(smem_u32(&sh.mma_done[s]), 1);
+    }
+    for (int s = 0; s < kGxRawStages; ++s) {
+      mbar_init(smem_u32(&sh.raw_full[s]), 1);
+      mbar_init(smem_u32(&sh.raw_empty[s]), 32 * kGxWarps);
+    }
+    mbar_init(smem_u32(&sh.tmem_full), 1);
+    sh.ctl.abort = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&map_g);
+    tma_prefetch_desc(&map_w);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&sh.tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sh.tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      for (int i = 0; i < k_steps; ++i) {
+        const int krow = (k_begin + i) * kGxRows;
+        const uint32_t s = i % kGxStages, ph = (i / kGxStages) & 1u;
+        if constexpr (CONVERT) {
+          const uint32_t rs = i % kGxRawStages, rph = (i / kGxRawStages) & 1u;
+          if (!mbar_wait(smem_u32(&sh.raw_empty[rs]), rph ^ 1u, &sh.ctl, p.status, 500 + (int)rs)) break;
+          const uint32_t rb = smem_u32(&sh.raw_full[rs]);
+          mbar_arrive_expect_tx(rb, kGxRawBytes);
+          // one box: [4 feature blocks][32 rows][64 B]
+          tma_load_3d(smem_u32(smem_r + rs * kGxRawBytes), &map_w, rb, 0, krow, c0 >> 6);
+        }
+        if (!mbar_wait(smem_u32(&sh.mma_done[s]), ph ^ 1u, &sh.ctl, p.status, 510 + (int)s)) break;
+        const uint32_t ab = smem_u32(&sh.a_full[s]);
+        mbar_arrive_expect_tx(ab, kGxABytes);
+        // one box: [4 batch blocks][32 rows][128 B], blocks beyond the batch are zero-filled
+        tma_load_3d(smem_u32(smem_a + s * kGxABytes), &map_g, ab, 0, krow, b0 >> 6);
+        if constexpr (!CONVERT) {
+          const uint32_t bb = smem_u32(&sh.b_full[s]);
+          mbar_arrive_expect_tx(bb, kGxBBytes);
+          tma_load_3d(smem_u32(smem_b + s * kGxBBytes), &map_w, bb, 0, krow, c0 >> 6);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(128, (uint32_t)n_eff, 1u, 1u, 1u, 1u);
+      bool ok = true;
+      for (int i = 0; i < k_steps; ++i) {
+        const uint32_t s = i % kGxStages, ph = (i / kGxStages) & 1u;
+        if (!mbar_wait(smem_u32(&sh.a_full[s]), ph, &sh.ctl, p.status, 520 + (int)s) ||
+            !mbar_wait(smem_u32(&sh.b_full[s]), ph, &sh.ctl, p.status, 530 + (int)s)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem_a + s * kGxABytes), sb = smem_u32(smem_b + s * kGxBBytes);
+        // MN-major, 128B swizzle: 64-element blocks kGxBlockBytes apart (leading offset), 8-row
+        // groups 1024 B apart (stride offset); one UMMA consumes 16 label rows = 2048 B per block
+        const uint64_t db = smem_desc_sw128(sb, kGxBlockBytes, 1024);
+        for (int hm = 0; hm < m_halves; ++hm) {
+          const uint64_t da = smem_desc_sw128(sa + hm * 2 * kGxBlockBytes, kGxBlockBytes, 1024);
+#pragma unroll
+          for (int u = 0; u < kGxRows / 16; ++u)
+            umma_f16(tmem_base + hm * 256, da + 128u * u, db + 128u * u, idesc, (i | u) != 0 ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&sh.mma_done[s]));
+      }
+      if (ok) umma_commit(smem_u32(&sh.tmem_full));
+    }
+  } else {
+    // -------------------- converters, then epilogue (warps 2..9) --------------------
+    const int cw = warp - 2, ct = cw * 32 + lane;                 // 0..255
+    bool ok = true;
+    if constexpr (CONVERT) {
+      for (int i = 0; i < k_steps && ok; ++i) {
+        const uint32_t s = i % kGxStages, ph = (i / kGxStages) & 1u;
+        const uint32_t rs = i % kGxRawStages, rph = (i / kGxRawStages) & 1u;
+        if (!mbar_wait(smem_u32(&sh.raw_full[rs]), rph, &sh.ctl, p.status, 540 + (int)rs) ||
+            !mbar_wait(smem_u32(&sh.mma_done[s]), ph ^ 1u, &sh.ctl, p.status, 550 + (int)s)) {
+          ok = false;
+          break;
+        }
+        // warp (block = cw & 3, row half = cw >> 2); per pass 8 rows x 64 B of one block: the reads
+        // are one contiguous 512 B run, the swizzled writes hit every bank equally often
+        const uint8_t* raw = smem_r + rs * kGxRawBytes + (cw & 3) * (kGxRows * 64);
+        uint8_t* dst = smem_b + s * kGxBBytes + (cw & 3) * kGxBlockBytes;
+#pragma unroll
+        for (int it = 0; it < 2; ++it) {
+          const int row = 16 * (cw >> 2) + 8 * it + (lane >> 2), kc = lane & 3;
+          const uint4 v = *reinterpret_cast<const uint4*>(raw + row * 64 + kc * 16);
+          uint4 o0, o1;
+          e4m3x4_to_bf16x4(v.x, o0.x, o0.y);
+          e4m3x4_to_bf16x4(v.y, o0.z, o0.w);
+          e4m3x4_to_bf16x4(v.z, o1.x, o1.y);
+          e4m3x4_to_bf16x4(v.w, o1.z, o1.w);
+          uint8_t* rowp = dst + row * 128;
+          *reinterpret_cast<uint4*>(rowp + (((2 * kc) ^ (row & 7)) << 4)) = o0;
+          *reinterpret_cast<uint4*>(rowp + (((2 * kc + 1) ^ (row & 7)) << 4)) = o1;
+        }
+        fence_proxy_async();                                      // generic-proxy writes -> tensor-core reads
+        mbar_arrive(smem_u32(&sh.b_full[s]));
+        mbar_arrive(smem_u32(&sh.raw_empty[rs]));
+      }
+    }
+    if (ok && mbar_wait(smem_u32(&sh.tmem_full), 0u, &sh.ctl, p.status, 560)) {
+      tc_fence_after();
+      const int q = warp & 3;
+      const int hm = cw >> 2;                                     // warps 2..5 -> accumulator 0, 6..9 -> 1
+      const int b = b0 + hm * 128 + q * 32 + lane;
+      const bool row_valid = b < p.bpad && hm < m_halves;
+      const bool have_acc = k_steps > 0;
+      if (have_acc || !p.accumulate) {
+        float* dstp = p.partial + ((size_t)split * p.bpad + b) * p.d + c0;
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + hm * 256;
+        for (int cg = 0; cg < n_eff; cg += 32) {
+          uint32_t v[32];
+          if (have_acc && hm < m_halves) {
+            tmem_ld32(taddr + cg, v);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0u;
+          }
+          if (!row_valid) continue;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            if (c0 + cg + 4 * i >= p.d) continue;
+            float4 o = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                   __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+            float4* ptr = reinterpret_cast<float4*>(dstp + cg + 4 * i);
+            if (p.accumulate) {
+              const float4 old = *ptr;
+              o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+            }
+            *ptr = o;
+          }
+        }
+      }
+    }
+  }
+
+  __syncwarp();
+  if (sh.ctl.abort) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace xmc

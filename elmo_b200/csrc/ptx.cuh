@@ -71,22 +71,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Wait limit for any single mbarrier wait.  Far above any legitimate wait (a whole kernel here
-// runs for well under 100 ms) and far below a watchdog.
-constexpr uint64_t kWaitLimitNs = 2000ull * 1000ull * 1000ull;
+// Wait limit for any single mbarrier wait, in SM clock cycles (~2 s at 2 GHz).  Far above any
+// legitimate wait (a whole kernel here runs for well under 100 ms) and far below a watchdog.
+// The SM-local cycle counter is used because it is cheap to read: waits sit on the critical path
+// of the producer/MMA hand-off, and the global nanosecond timer costs about a microsecond per read.
+constexpr long long kWaitLimitCycles = 4000000000ll;
 
 // Bounded wait.  Returns false if the CTA is aborting (this or another wait timed out).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Ctl* ctl, int* status,
                                           int where) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
+  const long long t0 = clock64();
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     ++spins;
-    if ((spins & 63u) == 0u) {
+    if ((spins & 255u) == 0u) {
       if (ctl->abort) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      if (clock64() - t0 > kWaitLimitCycles) {
         ctl->abort = 1;
         report(status, DEV_WAIT_TIMEOUT, where);
         return false;
@@ -104,6 +106,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
       "[%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_dst), "l"((uint64_t)map), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar,
+                                            int32_t c0, int32_t c1, int32_t c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_dst), "l"((uint64_t)map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {

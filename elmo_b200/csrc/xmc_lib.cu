@@ -6,12 +6,14 @@
 #include <algorithm>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
 #include "../../include/elmo_xmc.h"
 #include "aux_kernels.cuh"
 #include "gemm_engine.cuh"
+#include "gradx_kernel.cuh"
 #include "xmc_policies.cuh"
 
 namespace {
@@ -54,7 +56,7 @@ int get_encode(EncodeFn* out) {
 
 // 2-D row-major tensor [outer x inner], box [box_outer x box_inner], 128-byte swizzle, zero fill.
 int make_map(CUtensorMap* m, bool e4m3, const void* base, uint64_t inner, uint64_t outer,
-             uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer) {
+             uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, bool swizzle = true) {
   EncodeFn enc;
   if (int rc = get_encode(&enc)) return rc;
   if (((uintptr_t)base & 15u) != 0 || (row_stride_bytes & 15u) != 0)
@@ -66,12 +68,37 @@ int make_map(CUtensorMap* m, bool e4m3, const void* base, uint64_t inner, uint64
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = enc(m, e4m3 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
                          const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(XMC_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d): inner %llu outer %llu stride %llu box %ux%u",
                 (int)r, (unsigned long long)inner, (unsigned long long)outer,
                 (unsigned long long)row_stride_bytes, box_inner, box_outer);
+  return XMC_OK;
+}
+// [rows x cols] row-major matrix seen as [cols/64 blocks][rows][64 elements]: one box fetches
+// `box_rows` rows of 4 consecutive 64-element blocks, laid out block after block in shared memory
+// (each block = box_rows rows of 64 elements).  Blocks/rows outside the matrix read as zero.
+int make_map_blocked(CUtensorMap* m, bool e4m3, const void* base, uint64_t cols, uint64_t rows,
+                     uint64_t row_stride_elems, uint32_t box_rows, bool swizzle) {
+  EncodeFn enc;
+  if (int rc = get_encode(&enc)) return rc;
+  const uint32_t es = e4m3 ? 1 : 2;
+  if (cols % 64 != 0) return fail(XMC_ERR_INVALID, "blocked tensor map needs a multiple of 64 columns, got %llu", (unsigned long long)cols);
+  if (((uintptr_t)base & 15u) != 0 || ((row_stride_elems * es) & 15u) != 0)
+    return fail(XMC_ERR_INVALID, "tensor base/stride must be 16-byte aligned");
+  const cuuint64_t dims[3] = {64, rows, cols / 64};
+  const cuuint64_t strides[2] = {row_stride_elems * es, 64ull * es};
+  const cuuint32_t box[3] = {64, box_rows, 4};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = enc(m, e4m3 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                         const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(XMC_ERR_CUDA, "cuTensorMapEncodeTiled (blocked) failed (%d): cols %llu rows %llu stride %llu",
+                (int)r, (unsigned long long)cols, (unsigned long long)rows, (unsigned long long)row_stride_elems);
   return XMC_OK;
 }
 // operand whose K runs along the rows' contiguous direction
@@ -80,10 +107,10 @@ int make_map_kmajor(CUtensorMap* m, bool e4m3, const void* base, uint64_t k_elem
   const uint32_t es = e4m3 ? 1 : 2;
   return make_map(m, e4m3, base, k_elems, rows, row_stride_elems * es, 128 / es, box_rows);
 }
-// bf16 operand stored [k_rows x mn] (MN contiguous): boxes of 64 k-rows x 64 elements
+// bf16 operand stored [k_rows x mn] (MN contiguous): boxes of box_rows k-rows x 64 elements
 int make_map_mnmajor(CUtensorMap* m, const void* base, uint64_t mn, uint64_t k_rows,
-                     uint64_t row_stride_elems) {
-  return make_map(m, false, base, mn, k_rows, row_stride_elems * 2, 64, 64);
+                     uint64_t row_stride_elems, uint32_t box_rows = 64) {
+  return make_map(m, false, base, mn, k_rows, row_stride_elems * 2, 64, box_rows);
 }
 
 template <class Policy>
@@ -131,6 +158,7 @@ struct xmc_handle {
   int* status = nullptr;           // 4 ints
   int64_t ws_bytes = 0;
   // bookkeeping for the bench: kernels launched so far, optional per-kernel-class event timing
+  int64_t l2_persist_bytes = 0;    // size of the persisting-L2 carve-out this process asked for (0 = none)
   int64_t launches = 0;
   bool profile = false;
   std::vector<cudaEvent_t> ev_pool;
@@ -212,7 +240,7 @@ const char* xmc_version(void) { return "elmo_xmc sm_100a " __DATE__; }
 int xmc_create(const xmc_config* cfg, xmc_handle** out) {
   if (cfg == nullptr || out == nullptr) return fail(XMC_ERR_INVALID, "null argument");
   *out = nullptr;
-  if (cfg->dim <= 0 || cfg->dim % 16 != 0) return fail(XMC_ERR_INVALID, "dim must be a positive multiple of 16, got %d", cfg->dim);
+  if (cfg->dim <= 0 || cfg->dim % 64 != 0) return fail(XMC_ERR_INVALID, "dim must be a positive multiple of 64, got %d", cfg->dim);
   if (cfg->max_batch <= 0 || cfg->max_batch > 65535) return fail(XMC_ERR_INVALID, "max_batch must be in [1, 65535], got %d", cfg->max_batch);
   if (cfg->mode < XMC_MODE_BF16 || cfg->mode > XMC_MODE_SIMFP8) return fail(XMC_ERR_INVALID, "unknown mode %d", cfg->mode);
   if (!(cfg->w_scale > 0.f)) return fail(XMC_ERR_INVALID, "w_scale must be positive");
@@ -228,7 +256,7 @@ int xmc_create(const xmc_config* cfg, xmc_handle** out) {
   xmc_handle* h = new xmc_handle();
   h->cfg = *cfg;
   h->sm_count = prop.multiProcessorCount;
-  h->bpad_max = (int)round_up(cfg->max_batch, 16);
+  h->bpad_max = (int)round_up(cfg->max_batch, 64);
   if (cfg->sched_labels > 0) {
     h->sched = (int)cfg->sched_labels;
   } else {
@@ -246,8 +274,8 @@ int xmc_create(const xmc_config* cfg, xmc_handle** out) {
   A((void**)&h->x16, xrows * d * 2, true);
   A((void**)&h->xt, (size_t)std::max(d, 256) * h->bpad_max * 2, true);
   A((void**)&h->G, (size_t)h->sched * h->bpad_max * 2, true);
-  if (cfg->mode != XMC_MODE_BF16) A((void**)&h->w16, (size_t)h->sched * d * 2, true);
-  h->partial_floats = std::max<int64_t>((int64_t)h->sm_count * 128 * 256, (int64_t)h->bpad_max * round_up(d, 256));
+  if (cfg->mode == XMC_MODE_SIMFP8) A((void**)&h->w16, (size_t)h->sched * d * 2, true);
+  h->partial_floats = std::max<int64_t>((int64_t)h->sm_count * 256 * 256, (int64_t)h->bpad_max * round_up(d, 256));
   A((void**)&h->partial, (size_t)h->partial_floats * 4, true);
   A((void**)&h->status, 4 * sizeof(int), true);
   h->ent_cap = std::max<int64_t>(4096, (int64_t)cfg->max_batch * 64);
@@ -255,6 +283,12 @@ int xmc_create(const xmc_config* cfg, xmc_handle** out) {
   if (rc != XMC_OK) {
     xmc_destroy(h);
     return rc;
+  }
+  // per-process L2 carve-out for the partial sums (a context limit: it ends with the process)
+  if (getenv("XMC_NO_L2_PERSIST") == nullptr && prop.persistingL2CacheMaxSize > 0) {
+    const size_t want = std::min<size_t>((size_t)h->partial_floats * 4, (size_t)prop.persistingL2CacheMaxSize);
+    if (cudaDeviceSetLimit(cudaLimitPersistingL2CacheSize, want) == cudaSuccess) h->l2_persist_bytes = (int64_t)want;
+    else cudaGetLastError();
   }
   *out = h;
   return XMC_OK;
@@ -336,7 +370,7 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
   DeviceGuard guard(h->cfg.device);
   cudaStream_t st = (cudaStream_t)stream;
   const int d = h->cfg.dim, mode = h->cfg.mode;
-  const int bpad = (int)round_up(batch, 16);
+  const int bpad = (int)round_up(batch, 64);   // G rows are fetched in blocks of 64 batch columns
   const bool w8 = mode != XMC_MODE_BF16;
   const bool fwd_fp8 = mode == XMC_MODE_FP8;
   const bool want_loss = (flags & XMC_STEP_COMPUTE_LOSS) != 0;
@@ -372,10 +406,24 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
   }
 
   // --- grad_X partial geometry ---
-  const int n_bt = cdiv(bpad, 128), n_dt = cdiv(d, 256);
+  const int n_bt = cdiv(bpad, 256), n_dt = cdiv(d, 256);
   int n_splits = std::max(1, h->sm_count / (n_bt * n_dt));
   while (n_splits > 1 && (int64_t)n_splits * bpad * d > h->partial_floats) --n_splits;
   if ((int64_t)n_splits * bpad * d > h->partial_floats) return fail(XMC_ERR_STATE, "grad_X workspace too small");
+
+  // Keep the grad_X partial sums resident in L2 across the chunk launches of this step: every
+  // grad_X launch re-reads and re-writes them, and the weights/G streaming through L2 in between
+  // would otherwise push them out to HBM each time.  The window covers only this private buffer.
+  if (h->l2_persist_bytes > 0) {
+    cudaStreamAttrValue attr;
+    memset(&attr, 0, sizeof(attr));
+    attr.accessPolicyWindow.base_ptr = h->partial;
+    attr.accessPolicyWindow.num_bytes = std::min<size_t>((size_t)n_splits * bpad * d * 4, (size_t)h->l2_persist_bytes);
+    attr.accessPolicyWindow.hitRatio = 1.0f;
+    attr.accessPolicyWindow.hitProp = cudaAccessPropertyPersisting;
+    attr.accessPolicyWindow.missProp = cudaAccessPropertyStreaming;
+    CU_TRY(cudaStreamSetAttribute(st, cudaStreamAttributeAccessPolicyWindow, &attr));
+  }
 
   // --- operand maps that do not change across chunks ---
   CUtensorMap map_x, map_xt, map_g_k, map_g_mn;
@@ -387,7 +435,7 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
   }
   if (int rc = make_map_kmajor(&map_xt, false, h->xt, bpad, std::max(d, 256), bpad, 256)) return rc;
   if (int rc = make_map_kmajor(&map_g_k, false, h->G, bpad, h->sched, bpad, 128)) return rc;
-  if (int rc = make_map_mnmajor(&map_g_mn, h->G, bpad, h->sched, bpad)) return rc;
+  if (int rc = make_map_blocked(&map_g_mn, false, h->G, bpad, h->sched, bpad, xmc::kGxRows, true)) return rc;
 
   const float lr_eff = lr / h->cfg.w_scale;
   const int tiles_per_sched = h->sched / 128;
@@ -407,7 +455,7 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
 
       // bf16 view of the chunk's weights for the bf16 contractions
       const __nv_bfloat16* w16 = reinterpret_cast<const __nv_bfloat16*>(wbase);
-      if (w8) {
+      if (mode == XMC_MODE_SIMFP8) {   // only the simulated-FP8 forward needs a bf16 copy of the chunk
         const long long n16 = (long long)rows_valid * d / 16;
         const int blocks = (int)std::min<long long>((n16 + 255) / 256, (long long)h->sm_count * 8);
         mark(h, K_CONVERT, st);
@@ -452,20 +500,35 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
       if (rc) return rc;
 
       // grad_X partials: uses the pre-update weights (reference: chunked.py:116 precedes :119-127)
-      CUtensorMap map_w_mn;
-      if (int rc2 = make_map_mnmajor(&map_w_mn, w16, d, rows_valid, d)) return rc2;
-      xmc::GradXParams gp;
+      CUtensorMap map_w_gx;
+      if (w8) {
+        // raw e4m3 rows, unswizzled boxes of 32 rows x 256 features; converted inside the kernel
+        if (int rc2 = make_map_blocked(&map_w_gx, true, wbase, d, rows_valid, d, xmc::kGxRows, false)) return rc2;
+      } else {
+        if (int rc2 = make_map_blocked(&map_w_gx, false, wbase, d, rows_valid, d, xmc::kGxRows, true)) return rc2;
+      }
+      xmc::GxParams gp;
       gp.bpad = bpad;
       gp.d = d;
       gp.n_btiles = n_bt;
       gp.n_dtiles = n_dt;
       gp.n_splits = n_splits;
-      gp.total_ksteps = cdiv(rows_valid, 64);
+      gp.total_ksteps = cdiv(rows_valid, xmc::kGxRows);
       gp.accumulate = first ? 0 : 1;
       gp.partial = h->partial;
       gp.status = h->status;
       mark(h, K_GRADX, st);
-      if ((rc = launch_gemm<xmc::GradXPolicy>(map_g_mn, map_w_mn, gp, n_bt * n_dt * n_splits, h->sm_count, st))) return rc;
+      {
+        const int grid = n_bt * n_dt * n_splits;
+        if (w8) {
+          CU_TRY(cudaFuncSetAttribute(xmc::gradx_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, xmc::kGxSmemBytes));
+          xmc::gradx_kernel<true><<<grid, xmc::kGxThreads, xmc::kGxSmemBytes, st>>>(map_g_mn, map_w_gx, gp);
+        } else {
+          CU_TRY(cudaFuncSetAttribute(xmc::gradx_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, xmc::kGxSmemBytes));
+          xmc::gradx_kernel<false><<<grid, xmc::kGxThreads, xmc::kGxSmemBytes, st>>>(map_g_mn, map_w_gx, gp);
+        }
+        CU_TRY(cudaGetLastError());
+      }
 
       // fused dW + SGD update of the chunk, in place
       xmc::UpdParams up;
@@ -555,12 +618,16 @@ int xmc_forward_topk(xmc_handle*, const void*, int32_t, int32_t, int32_t, int64_
 int xmc_test_gemm(int32_t device, int32_t layout, int32_t dtype, int32_t M, int32_t N, int32_t K,
                   const void* A, const void* B, float* D, void* stream) {
   if (A == nullptr || B == nullptr || D == nullptr || M <= 0 || N <= 0 || K <= 0) return fail(XMC_ERR_INVALID, "bad argument");
-  if (layout == 1 && dtype != XMC_DT_BF16) return fail(XMC_ERR_INVALID, "MN-major test takes bf16");
+  if ((layout & 1) == 1 && dtype != XMC_DT_BF16) return fail(XMC_ERR_INVALID, "MN-major test takes bf16");
   if (dtype != XMC_DT_BF16 && dtype != XMC_DT_E4M3) return fail(XMC_ERR_INVALID, "dtype");
   DeviceGuard guard(device);
-  cudaDeviceProp prop;
-  CU_TRY(cudaGetDeviceProperties(&prop, device));
-  if (prop.major != 10) return fail(XMC_ERR_CUDA, "device is not sm_100");
+  int cc_major = 0, sm_count = 0;
+  CU_TRY(cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, device));
+  CU_TRY(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
+  if (cc_major != 10) return fail(XMC_ERR_CUDA, "device is not sm_100");
+  // XMC_TEST_GEMM_REPEAT=n launches the contraction n times back to back (throughput probes)
+  const char* rep_env = getenv("XMC_TEST_GEMM_REPEAT");
+  const int repeat = rep_env ? std::max(1, atoi(rep_env)) : 1;
   int* status = nullptr;
   CU_TRY(cudaMalloc((void**)&status, 16));
   CU_TRY(cudaMemset(status, 0, 16));
@@ -572,19 +639,23 @@ int xmc_test_gemm(int32_t device, int32_t layout, int32_t dtype, int32_t M, int3
   p.n_mtiles = cdiv(M, 128);
   p.n_ntiles = cdiv(N, 256);
   p.D = D;
+  p.checksum_only = (layout & 2) ? 1 : 0;
+  layout &= 1;
   p.status = status;
-  int rc;
+  int rc = XMC_OK;
   if (layout == 0) {
     if ((rc = make_map_kmajor(&ma, f8, A, K, M, K, 128))) { cudaFree(status); return rc; }
     if ((rc = make_map_kmajor(&mb, f8, B, K, N, K, 256))) { cudaFree(status); return rc; }
     p.k_steps = cdiv((long long)K * (f8 ? 1 : 2), 128);
-    rc = f8 ? launch_gemm<xmc::PlainPolicy<true, false>>(ma, mb, p, p.n_mtiles * p.n_ntiles, prop.multiProcessorCount, st)
-            : launch_gemm<xmc::PlainPolicy<false, false>>(ma, mb, p, p.n_mtiles * p.n_ntiles, prop.multiProcessorCount, st);
+    for (int r = 0; r < repeat && rc == XMC_OK; ++r)
+      rc = f8 ? launch_gemm<xmc::PlainPolicy<true, false>>(ma, mb, p, p.n_mtiles * p.n_ntiles, sm_count, st)
+              : launch_gemm<xmc::PlainPolicy<false, false>>(ma, mb, p, p.n_mtiles * p.n_ntiles, sm_count, st);
   } else {
     if ((rc = make_map_mnmajor(&ma, A, M, K, M))) { cudaFree(status); return rc; }
     if ((rc = make_map_mnmajor(&mb, B, N, K, N))) { cudaFree(status); return rc; }
     p.k_steps = cdiv(K, 64);
-    rc = launch_gemm<xmc::PlainPolicy<false, true>>(ma, mb, p, p.n_mtiles * p.n_ntiles, prop.multiProcessorCount, st);
+    for (int r = 0; r < repeat && rc == XMC_OK; ++r)
+      rc = launch_gemm<xmc::PlainPolicy<false, true>>(ma, mb, p, p.n_mtiles * p.n_ntiles, sm_count, st);
   }
   if (rc == XMC_OK) {
     cudaError_t e = cudaStreamSynchronize(st);

@@ -424,6 +424,7 @@ struct PlainParams {
   int n_mtiles, n_ntiles;
   int k_steps;
   float* D;                // [M x N]
+  int checksum_only;       // 1: do not store D (times the main loop without the output traffic)
   int* status;
 };
 
@@ -462,10 +463,23 @@ struct PlainPolicy {
         for (int i = 0; i < 32; ++i) v[i] = 0u;
       }
       if (m >= p.M) continue;
+      if (p.checksum_only) {          // main-loop timing: fold the tile into one word per thread
+        uint32_t x = 0;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const int n = j.b0 + c0 + i;
-        if (n < p.N) p.D[(size_t)m * p.N + n] = __uint_as_float(v[i]);
+        for (int i = 0; i < 32; ++i) x ^= v[i];
+        if (x == 0x12345678u) p.D[0] = 1.f;
+        continue;
+      }
+      float* drow = p.D + (size_t)m * p.N + j.b0 + c0;
+      if ((p.N & 3) == 0 && j.b0 + c0 + 32 <= p.N) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          reinterpret_cast<float4*>(drow)[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                                           __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (j.b0 + c0 + i < p.N) drow[i] = __uint_as_float(v[i]);
       }
     }
   }

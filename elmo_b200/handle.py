@@ -138,7 +138,7 @@ class XmcHandle:
 def test_gemm(a: torch.Tensor, b: torch.Tensor, layout: int) -> torch.Tensor:
     """D = A B^T on the library's tensor-core engine (self-test hook of the C ABI)."""
     lib = _lib.load()
-    if layout == 0:
+    if (layout & 1) == 0:
         (m, k), (n, _) = a.shape, b.shape
     else:
         (k, m), (_, n) = a.shape, b.shape

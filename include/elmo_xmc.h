@@ -62,7 +62,7 @@ typedef struct xmc_handle xmc_handle;
 
 typedef struct {
   int32_t device;          /* CUDA device ordinal                                              */
-  int32_t dim;             /* d, features per label row; multiple of 16                        */
+  int32_t dim;             /* d, features per label row; multiple of 64                        */
   int32_t max_batch;       /* largest B a step will see (<= 65535)                             */
   int32_t mode;            /* XMC_MODE_*                                                       */
   int64_t label_offset;    /* global id of this handle's first label row (label-range shards)  */
@@ -150,6 +150,7 @@ const char* xmc_version(void);
  * engine, to validate the tensor-core path in isolation.
  *   layout 0: A [M x K], B [N x K] both K-major (row-major as written), dtype XMC_DT_BF16 or XMC_DT_E4M3
  *   layout 1: A given as [K x M], B as [K x N] row-major (both "MN-major"), dtype XMC_DT_BF16
+ *   layout | 2: same contraction, but D is not stored (times the main loop alone)
  * M, N, K arbitrary positive (rows 16-byte aligned: inner extents multiples of 8 (bf16) / 16 (e4m3)).
  */
 int xmc_test_gemm(int32_t device, int32_t layout, int32_t dtype, int32_t M, int32_t N, int32_t K,

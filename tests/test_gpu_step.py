@@ -78,6 +78,20 @@ def test_fp8_step_matches_oracle(L, d, B, nc, sched, rounding):
     assert changed > 0                                                # the step did update weights
 
 
+def test_fp8_step_with_subnormal_weights():
+    """Most stored weights below 2^-6 (e4m3 subnormals): exercises the in-kernel e4m3 -> bf16
+    operand conversion of grad_X and stochastic rounding on the uniform part of the grid."""
+    from oracle import xmc_oracle as O
+    L, d, B = 2304, 192, 272
+    w, x, lab = _inputs(L, d, B, 900, seed=77, w_std=0.008)
+    assert float((w.float().abs() < 2.0 ** -6).float().mean()) > 0.8
+    for rounding in ("rn", "sr"):
+        want_w, want_gx, _ = O.fp8_chunked_step([w], x, lab, 2.0, rounding=rounding, seed=5, step=9)
+        got_w, g32, _, _ = _run_gpu("fp8", [w], x, lab, 2.0, stochastic=(rounding == "sr"), step=9, sched=1024)
+        _check_weights(got_w, want_w)
+        assert rel_inf(g32, want_gx) < 1e-2
+
+
 def test_fp8_step_with_scale_and_tiny_weights():
     """Xavier-sized weights sit below e4m3's normal range at scale 1; with w_scale they train."""
     from oracle import xmc_oracle as O
