@@ -608,8 +608,68 @@ int xmc_profile(xmc_handle* h, int32_t enable, double* ms_by_kind, int64_t* laun
   return XMC_OK;
 }
 
-int xmc_forward_logits(xmc_handle*, const void*, int32_t, int32_t, void*, int64_t, int64_t, void*) {
-  return fail(XMC_ERR_STATE, "xmc_forward_logits: not built yet");
+int xmc_forward_logits(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, void* out_bf16,
+                       int64_t ld_out, int64_t n_out, void* stream) {
+  if (h == nullptr || x == nullptr || out_bf16 == nullptr) return fail(XMC_ERR_INVALID, "null argument");
+  if (h->w_ptrs.empty()) return fail(XMC_ERR_STATE, "xmc_bind_weights has not been called");
+  if (x_dtype != XMC_DT_BF16 && x_dtype != XMC_DT_E4M3) return fail(XMC_ERR_INVALID, "embeddings must be bf16 or e4m3");
+  if (batch <= 0 || batch > h->cfg.max_batch) return fail(XMC_ERR_INVALID, "batch %d outside [1, %d]", batch, h->cfg.max_batch);
+  if (n_out <= 0 || n_out > h->total_rows || ld_out < n_out || (ld_out & 7) || ((uintptr_t)out_bf16 & 15u))
+    return fail(XMC_ERR_INVALID, "bad output geometry (n_out %lld, ld_out %lld, rows %lld)", (long long)n_out, (long long)ld_out, (long long)h->total_rows);
+  DeviceGuard guard(h->cfg.device);
+  cudaStream_t st = (cudaStream_t)stream;
+  const int d = h->cfg.dim, mode = h->cfg.mode;
+  const int bpad = (int)round_up(batch, 64);
+  const bool fwd_fp8 = mode == XMC_MODE_FP8;
+  if (int rc = prep_x(h, x, x_dtype, batch, bpad, fwd_fp8, !fwd_fp8, false, st)) return rc;
+  CUtensorMap map_x;
+  const size_t xrows = (size_t)std::max(h->bpad_max, 256);
+  if (fwd_fp8) {
+    if (int rc = make_map_kmajor(&map_x, true, h->x8, d, xrows, d, 128)) return rc;
+  } else {
+    if (int rc = make_map_kmajor(&map_x, false, h->x16, d, xrows, d, 128)) return rc;
+  }
+  int64_t row_base = 0;
+  for (size_t wc = 0; wc < h->w_ptrs.size() && row_base < n_out; ++wc) {
+    const int64_t rows_wc = h->w_rows[wc];
+    for (int64_t s0 = 0; s0 < rows_wc && row_base + s0 < n_out; s0 += h->sched) {
+      const int rows = (int)std::min<int64_t>(h->sched, rows_wc - s0);
+      const size_t esz = mode == XMC_MODE_BF16 ? 2 : 1;
+      const uint8_t* wbase = reinterpret_cast<const uint8_t*>(h->w_ptrs[wc]) + (size_t)s0 * d * esz;
+      const void* wsrc = wbase;
+      if (mode == XMC_MODE_SIMFP8) {
+        const long long n16 = (long long)rows * d / 16;
+        const int blocks = (int)std::min<long long>((n16 + 255) / 256, (long long)h->sm_count * 8);
+        mark(h, K_CONVERT, st);
+        xmc::e4m3_to_bf16_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const uint4*>(wbase),
+                                                         reinterpret_cast<uint4*>(h->w16), n16);
+        CU_TRY(cudaGetLastError());
+        wsrc = h->w16;
+      }
+      CUtensorMap map_w;
+      if (int rc = make_map_kmajor(&map_w, fwd_fp8, wsrc, d, rows, d, 256)) return rc;
+      xmc::LogitsParams lp;
+      lp.batch = batch;
+      lp.rows = rows;
+      lp.n_mtiles = cdiv(batch, 128);
+      lp.n_ntiles = cdiv(rows, 256);
+      lp.k_steps = cdiv((long long)d * (fwd_fp8 ? 1 : 2), 128);
+      lp.w_scale = h->cfg.w_scale;
+      lp.out = reinterpret_cast<__nv_bfloat16*>(out_bf16);
+      lp.ld_out = ld_out;
+      lp.col0 = row_base + s0;
+      lp.n_out = n_out;
+      lp.status = h->status;
+      mark(h, K_LOGITS, st);
+      const int tiles = lp.n_mtiles * lp.n_ntiles;
+      const int rc = fwd_fp8 ? launch_gemm<xmc::LogitsPolicy<true>>(map_x, map_w, lp, tiles, h->sm_count, st)
+                             : launch_gemm<xmc::LogitsPolicy<false>>(map_x, map_w, lp, tiles, h->sm_count, st);
+      if (rc) return rc;
+    }
+    row_base += rows_wc;
+  }
+  mark(h, K_END, st);
+  return XMC_OK;
 }
 int xmc_forward_topk(xmc_handle*, const void*, int32_t, int32_t, int32_t, int64_t, float*, int32_t*, void*) {
   return fail(XMC_ERR_STATE, "xmc_forward_topk: not built yet");

@@ -1,7 +1,7 @@
 // GEMM policies (tile mapping + epilogue) of the chunked XMC step:
 //   FwdPolicy    Z^T[labels x batch] = W X^T  ->  G = sigmoid(Z) - Y  (bf16, label-major), loss terms
 //   UpdPolicy    acc[labels x d] = G X        ->  W <- round(W - lr*(acc + wd*W))   (dW never stored)
-//   GradXPolicy  partial[batch x d] (+)= G^T W  over a slice of the chunk's label rows
+//   LogitsPolicy out[batch x labels] = bf16(X W^T)  (inference forward)
 //   PlainPolicy  D = A B^T (engine self-test)
 #pragma once
 #include "gemm_engine.cuh"
@@ -345,40 +345,40 @@ struct UpdPolicy {
 };
 
 // -------------------------------------------------------------------------------------------------
-// grad_X partial sums (reference: matmul_kernel.py:204-239 large_k_matmul: C = G^T W, both operands
-// bf16, fp32 accumulation).  Each (split, batch tile, d tile) owns one slot of `partial` and adds to
-// it in chunk order, so the summation order is fixed (no atomics).
+// Inference logits (reference: chunked.py:48-53, chunked_fp8xmc_clf.py:45-60 xfc_forward):
+// out[b][col0 + r] = bf16(w_scale * <x[b], W[r]>).  Batch rows sit on the TMEM lanes so that a thread
+// stores runs of consecutive labels.
 // -------------------------------------------------------------------------------------------------
-struct GradXParams {
-  int bpad, d;
-  int n_btiles, n_dtiles, n_splits;
-  int total_ksteps;        // cdiv(rows written by the forward kernel, 64)
-  int accumulate;          // 0: overwrite the slot (first chunk of a step)
-  float* partial;          // [n_splits][bpad][d]
+struct LogitsParams {
+  int batch, rows;         // valid batch rows, label rows of this launch
+  int n_mtiles, n_ntiles;  // batch tiles of 128, label tiles of 256
+  int k_steps;
+  float w_scale;
+  __nv_bfloat16* out;      // [batch x ld_out]
+  long long ld_out;
+  long long col0;          // column of this launch's label row 0
+  long long n_out;         // columns >= n_out are not written
   int* status;
 };
 
-struct GradXPolicy {
-  using Params = GradXParams;
-  static constexpr bool kMnMajor = true;
-  static constexpr bool kFp8 = false;
-  static constexpr uint32_t kFmt = 1u;
-  static constexpr int kElemsPerRow = 64;
-  static constexpr int kEpiWarps = 4;
+template <bool FP8>
+struct LogitsPolicy {
+  using Params = LogitsParams;
+  static constexpr bool kMnMajor = false;
+  static constexpr bool kFp8 = FP8;
+  static constexpr uint32_t kFmt = FP8 ? 0u : 1u;
+  static constexpr int kElemsPerRow = FP8 ? 128 : 64;
+  static constexpr int kEpiWarps = 8;
   using EpilogueState = NoState;
-
-  __device__ static int num_tiles(const Params& p) { return p.n_btiles * p.n_dtiles * p.n_splits; }
+  __device__ static int num_tiles(const Params& p) { return p.n_mtiles * p.n_ntiles; }
   __device__ static void job(const Params& p, int tile, Job& j) {
-    const int per = p.n_btiles * p.n_dtiles;
-    j.t2 = tile / per;                      // split
-    const int r = tile - j.t2 * per;
-    j.t0 = r / p.n_dtiles;                  // batch tile
-    j.t1 = r - j.t0 * p.n_dtiles;           // d tile
+    j.t1 = tile / p.n_mtiles;            // label tile (adjacent CTAs share it)
+    j.t0 = tile - j.t1 * p.n_mtiles;     // batch tile
     j.a0 = j.t0 * kTileM;
     j.b0 = j.t1 * kTileN;
-    j.k_begin = (int)(((long long)j.t2 * p.total_ksteps) / p.n_splits);
-    j.k_steps = (int)(((long long)(j.t2 + 1) * p.total_ksteps) / p.n_splits) - j.k_begin;
-    j.n_eff = min(kTileN, round_up16(p.d - j.b0));
+    j.k_begin = 0;
+    j.k_steps = p.k_steps;
+    j.n_eff = min(kTileN, round_up16(p.rows - j.b0));
   }
   __device__ static void epilogue_begin(const Params&, EpilogueState&) {}
   __device__ static void epilogue_pre(const Params&, const Job&, SharedTail&, const EpiCtx&, EpilogueState&) {}
@@ -386,9 +386,6 @@ struct GradXPolicy {
   __device__ static void epilogue(const Params& p, const Job& j, uint32_t taddr, bool have_acc,
                                   SharedTail&, const EpiCtx& ec, EpilogueState&) {
     const int b = j.a0 + ec.q * 32 + ec.lane;
-    const bool row_valid = b < p.bpad;
-    if (!have_acc && p.accumulate) return;
-    float* dst = p.partial + ((size_t)j.t2 * p.bpad + b) * p.d + j.b0;
     for (int c0 = 32 * ec.h; c0 < j.n_eff; c0 += 32 * ec.nsplit) {
       uint32_t v[32];
       if (have_acc) {
@@ -398,19 +395,21 @@ struct GradXPolicy {
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = 0u;
       }
-      if (!row_valid) continue;
+      if (b >= p.batch) continue;
+      const long long col = p.col0 + j.b0 + c0;
+      const int valid = (int)max(0ll, min(32ll, min((long long)(p.rows - j.b0 - c0), p.n_out - col)));
+      __nv_bfloat16* dst = p.out + (size_t)b * p.ld_out + col;
+      uint32_t o[16];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int col = j.b0 + c0 + 4 * i;
-        if (col >= p.d) continue;
-        float4 o = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
-                               __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
-        float4* ptr = reinterpret_cast<float4*>(dst + c0 + 4 * i);
-        if (p.accumulate) {
-          const float4 old = *ptr;
-          o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-        }
-        *ptr = o;
+      for (int i = 0; i < 16; ++i)
+        o[i] = pack_bf16x2(__uint_as_float(v[2 * i]) * p.w_scale, __uint_as_float(v[2 * i + 1]) * p.w_scale);
+      if (valid == 32 && (((uintptr_t)dst) & 15u) == 0) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          reinterpret_cast<uint4*>(dst)[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+      } else {
+        const uint16_t* h16 = reinterpret_cast<const uint16_t*>(o);
+        for (int i = 0; i < valid; ++i) reinterpret_cast<uint16_t*>(dst)[i] = h16[i];
       }
     }
   }

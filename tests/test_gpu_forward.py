@@ -1,0 +1,104 @@
+"""xfc_forward (inference logits) of the CUDA classes against the reference's own outputs
+(golden fixtures produced by the unmodified reference on CPU) and against the oracle."""
+from types import SimpleNamespace as NS
+
+import pytest
+import torch
+
+from tests._util import as_bf16, as_e4m3, load_golden, rel_inf
+
+pytestmark = pytest.mark.gpu
+
+
+def _cfg(L, d, B, nc, sim=False, dtype="bfloat16"):
+    return NS(environment=NS(device="cuda:0"),
+              model=NS(xmc=NS(dtype=dtype, num_chunks=nc, input_features=d)),
+              training=NS(precision=NS(mode="mixed", purelp_dtype="bfloat16"),
+                          xmc=NS(momentum=0, wd=0.0, simulated_fp8=sim)),
+              data=NS(num_labels=L, batch_size=B))
+
+
+@pytest.mark.parametrize("tag,sim", [("real", False), ("sim", True)])
+def test_fp8_forward_matches_reference_fixture(tag, sim):
+    from elmo_b200.xmc_classifiers import Fp8XMCBCEChunkedLayer
+    g = load_golden("fp8_forward.npz")
+    L, d, B, nc = int(g["L"]), int(g["d"]), int(g["B"]), int(g["nc"])
+    layer = Fp8XMCBCEChunkedLayer(_cfg(L, d, B, nc, sim))
+    assert layer.num_labels == int(g["L_padded"]) and layer.num_labels_i == int(g["L_i"])
+    for i in range(nc):
+        layer.xfc_weight[i].data.copy_(as_e4m3(g[f"{tag}_w{i}"]))
+    x = as_bf16(g[f"{tag}_x"]).cuda()
+    z = layer.xfc_forward(x).cpu()
+    ref = as_bf16(g[f"{tag}_logits"])
+    assert z.shape == ref.shape == (B, L)
+    same = (z.view(torch.int16) == ref.view(torch.int16)).float().mean()
+    assert same >= 0.99, same                       # tensor-core vs CPU accumulation order
+    assert rel_inf(z, ref) < 1e-2
+    # the evaluator hands in e4m3-cast embeds (evaluate.py:155-156)
+    z8 = layer.xfc_forward(x.to(torch.float8_e4m3fn)).cpu()
+    assert rel_inf(z8, as_bf16(g[f"{tag}_logits_e4m3_embed"])) < 1e-2
+    layer._handle.check()
+
+
+def test_bf16_forward_matches_reference_fixture():
+    from elmo_b200.xmc_classifiers import XMCBCECHUNKEDLayer
+    g = load_golden("chunked_bf16.npz")
+    L, d, B, nc = int(g["L"]), int(g["d"]), int(g["B"]), int(g["nc"])
+    layer = XMCBCECHUNKEDLayer(_cfg(L, d, B, nc))
+    layer.xfc_weight.copy_(as_bf16(g["w2"]))
+    z = layer.xfc_forward(as_bf16(g["x1"]).cuda()).cpu()
+    ref = as_bf16(g["logits_last"])
+    assert z.shape == ref.shape
+    assert rel_inf(z, ref) < 1e-2
+    layer._handle.check()
+
+
+def test_forward_large_odd_shapes_match_oracle():
+    from elmo_b200.xmc_classifiers import Fp8XMCBCEChunkedLayer
+    from oracle import xmc_oracle as O
+    L, d, B, nc = 70001, 256, 200, 3
+    layer = Fp8XMCBCEChunkedLayer(_cfg(L, d, B, nc))
+    gen = torch.Generator().manual_seed(0)
+    ws = []
+    for p in layer.xfc_weight:
+        w = (torch.randn(p.shape, generator=gen) * 0.25).to(torch.float8_e4m3fn)
+        p.data.copy_(w); ws.append(w)
+    x = (torch.randn(B - 3, d, generator=gen) / d ** 0.5).to(torch.bfloat16)     # short last batch
+    z = layer.xfc_forward(x.cuda()).cpu()
+    ref = O.forward_logits(ws, x, num_labels=L)
+    assert z.shape == ref.shape == (B - 3, L)
+    assert rel_inf(z, ref) < 1e-2
+    layer._handle.check()
+
+
+def test_layer_step_through_class_api_matches_oracle():
+    """The runner's call sequence (runner.py:146-157) on the drop-in class."""
+    from elmo_b200.xmc_classifiers import Fp8XMCBCEChunkedLayer
+    from oracle import xmc_oracle as O
+    L, d, B, nc = 3000, 128, 64, 2
+    cfg = _cfg(L, d, B, nc)
+    cfg.training.xmc.rounding = "rn"
+    layer = Fp8XMCBCEChunkedLayer(cfg)
+    gen = torch.Generator().manual_seed(3)
+    ws = []
+    for p in layer.xfc_weight:
+        w = (torch.randn(p.shape, generator=gen) * 0.25).to(torch.float8_e4m3fn)
+        p.data.copy_(w); ws.append(w)
+    for it in range(2):
+        x = (torch.randn(B, d, generator=gen) / d ** 0.5).to(torch.bfloat16)
+        lab = torch.stack([torch.randint(0, B, (200,), generator=gen),
+                           torch.randint(0, L, (200,), generator=gen)], 1).to(torch.int32)
+        loss = layer.xfc_forward_backward(x.cuda(), lab.cuda(), [0.5], skip_loss=(it == 0))
+        ws, gx, want_loss = O.fp8_chunked_step(ws, x, lab, 0.5, rounding="rn", compute_loss=True)
+        assert rel_inf(layer.grad_input.float().cpu(), gx) < 1e-2
+        if it == 1:
+            assert abs(loss - want_loss) < 1e-3 * abs(want_loss)
+        else:
+            assert loss == 0
+        layer.grad_input[0:B].div_(2)                       # the runner mutates it in place
+    for p, w in zip(layer.xfc_weight, ws):
+        assert (p.data.cpu().view(torch.uint8) == w.view(torch.uint8)).float().mean() >= 0.999
+    assert layer.iteration == 2
+    sd = layer.state_dict()
+    assert sorted(sd) == [f"xfc_weight.{i}" for i in range(nc)]
+    layer._handle.check()
