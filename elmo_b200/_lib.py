@@ -44,6 +44,8 @@ _SIGNATURES = {
     "xmc_profile": (C.c_int, [C.c_void_p, C.c_int32, C.POINTER(C.c_double), C.POINTER(C.c_int64)]),
     "xmc_last_error": (C.c_char_p, []),
     "xmc_version": (C.c_char_p, []),
+    "xmc_large_k_matmul_noalloc": (C.c_int, [C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
+                                             C.c_int32, C.c_void_p, C.c_void_p]),
     "xmc_test_gemm": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                 C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
 }

@@ -675,6 +675,79 @@ int xmc_forward_topk(xmc_handle*, const void*, int32_t, int32_t, int32_t, int64_
   return fail(XMC_ERR_STATE, "xmc_forward_topk: not built yet");
 }
 
+// ---------------------------------------------------------------------------------------------
+// Allocation-free contraction  C[m x n] = A^T B  (A given as [k x m] bf16, B as [k x n] bf16 or e4m3):
+// the grad_X kernel with its split-K partial sums kept in a fixed device array owned by the library.
+// ---------------------------------------------------------------------------------------------
+namespace {
+constexpr size_t kNoAllocFloats = 2u << 20;              // 8 MiB of partial sums
+constexpr int kNoAllocMaxDevices = 64;
+// [0, kNoAllocFloats): partial sums; then 4 ints of kernel status.  Every GPU that loads the library
+// carries one copy until the process exits.
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocFloats + 64];
+// Device addresses of the array, one per device, filled on the first call for that device.  In host
+// code the symbol itself is only a stand-in; the address a kernel can use comes from
+// cudaGetSymbolAddress with the device current.
+static float* g_noalloc_ptr[kNoAllocMaxDevices] = {nullptr};
+}  // namespace
+
+int xmc_large_k_matmul_noalloc(int32_t device, const void* a_bf16, const void* b, int32_t b_dtype,
+                               int32_t k, int32_t m, int32_t n, float* c_f32, void* stream) {
+  if (a_bf16 == nullptr || b == nullptr || c_f32 == nullptr) return fail(XMC_ERR_INVALID, "null argument");
+  if (b_dtype != XMC_DT_BF16 && b_dtype != XMC_DT_E4M3) return fail(XMC_ERR_INVALID, "b must be bf16 or e4m3");
+  if (k <= 0 || m <= 0 || n <= 0 || (m % 64) != 0 || (n % 64) != 0)
+    return fail(XMC_ERR_INVALID, "need k > 0 and m, n positive multiples of 64 (got k %d, m %d, n %d)", k, m, n);
+  if ((size_t)m * (size_t)n > kNoAllocFloats)
+    return fail(XMC_ERR_INVALID, "m*n = %lld exceeds the built-in scratch of %lld floats (8 MiB): use the handle-based API",
+                (long long)m * n, (long long)kNoAllocFloats);
+  if (((uintptr_t)c_f32 & 15u) != 0) return fail(XMC_ERR_INVALID, "c must be 16-byte aligned");
+  if (device < 0 || device >= kNoAllocMaxDevices) return fail(XMC_ERR_INVALID, "device %d out of range", device);
+  DeviceGuard guard(device);
+  if (g_noalloc_ptr[device] == nullptr) {
+    // set-up, once per device, with that device current (the guard above)
+    int cc_major = 0;
+    CU_TRY(cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, device));
+    if (cc_major != 10) return fail(XMC_ERR_CUDA, "device %d is not sm_100", device);
+    float* ptr = nullptr;
+    CU_TRY(cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch));
+    CU_TRY(cudaFuncSetAttribute(xmc::gradx_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, xmc::kGxSmemBytes));
+    CU_TRY(cudaFuncSetAttribute(xmc::gradx_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, xmc::kGxSmemBytes));
+    g_noalloc_ptr[device] = ptr;
+  }
+  float* scratch = g_noalloc_ptr[device];
+  int* status = reinterpret_cast<int*>(scratch + kNoAllocFloats);
+  int sm_count = 0;
+  CU_TRY(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool f8 = b_dtype == XMC_DT_E4M3;
+  CUtensorMap map_a, map_b;
+  if (int rc = make_map_blocked(&map_a, false, a_bf16, m, k, m, xmc::kGxRows, true)) return rc;
+  if (int rc = make_map_blocked(&map_b, f8, b, n, k, n, xmc::kGxRows, !f8)) return rc;
+  xmc::GxParams gp;
+  gp.bpad = m;
+  gp.d = n;
+  gp.n_btiles = cdiv(m, 256);
+  gp.n_dtiles = cdiv(n, 256);
+  const int tiles = gp.n_btiles * gp.n_dtiles;
+  int n_splits = std::max(1, sm_count / tiles);
+  n_splits = (int)std::min<size_t>((size_t)n_splits, kNoAllocFloats / ((size_t)m * n));
+  gp.total_ksteps = cdiv(k, xmc::kGxRows);
+  n_splits = std::max(1, std::min(n_splits, gp.total_ksteps));
+  gp.n_splits = n_splits;
+  gp.accumulate = 0;            // every slot in use is fully overwritten: nothing to clear but the status
+  gp.partial = scratch;
+  gp.status = status;
+  CU_TRY(cudaMemsetAsync(status, 0, 4 * sizeof(int), st));
+  if (f8) xmc::gradx_kernel<true><<<tiles * n_splits, xmc::kGxThreads, xmc::kGxSmemBytes, st>>>(map_a, map_b, gp);
+  else xmc::gradx_kernel<false><<<tiles * n_splits, xmc::kGxThreads, xmc::kGxSmemBytes, st>>>(map_a, map_b, gp);
+  CU_TRY(cudaGetLastError());
+  const long long total = (long long)m * n;
+  const int blocks = (int)std::min<long long>((total + 255) / 256, (long long)sm_count * 8);
+  xmc::reduce_gradx_kernel<<<blocks, 256, 0, st>>>(scratch, n_splits, m, m, n, 1.0f, c_f32, nullptr);
+  CU_TRY(cudaGetLastError());
+  return XMC_OK;
+}
+
 int xmc_test_gemm(int32_t device, int32_t layout, int32_t dtype, int32_t M, int32_t N, int32_t K,
                   const void* A, const void* B, float* D, void* stream) {
   if (A == nullptr || B == nullptr || D == nullptr || M <= 0 || N <= 0 || K <= 0) return fail(XMC_ERR_INVALID, "bad argument");

@@ -146,6 +146,27 @@ const char* xmc_last_error(void);
 const char* xmc_version(void);
 
 /*
+ * C[m x n] (fp32) = A^T B for A stored [k x m] bf16 and B stored [k x n] (bf16 or e4m3): the
+ * contraction over a very long k that grad_X needs, as a stand-alone call that ALLOCATES NOTHING.
+ * This entry point has no counterpart in the reference (its large_k_matmul allocates its output and
+ * runs wherever torch's allocator lets it).  It exists for callers that may not call cudaMalloc
+ * where they invoke the library: code running under a memory pool that owns the whole device, inside
+ * a region where allocation is forbidden (e.g. latency-critical serving loops), or plug-ins whose
+ * host hands them buffers and nothing else.  The split-k partial sums that the kernel normally keeps
+ * in a cudaMalloc'd workspace live in an 8 MiB array built into the library image instead (every GPU
+ * that loads the library holds it until the process exits).
+ *   - limit: m * n <= 2 097 152 (8 MiB of fp32); larger shapes are rejected with XMC_ERR_INVALID --
+ *     use the handle-based API for those.  m and n must be multiples of 64; c 16-byte aligned.
+ *   - the first call on a device looks up the array's device address and sets kernel attributes; make
+ *     that first call outside any stream capture.
+ *   - all calls share the one array and it keeps the last call's contents: two calls whose kernels
+ *     overlap on the GPU (different streams) race.  Serialise them on one stream.
+ *   - asynchronous on `stream`; neither cudaMalloc/cudaFree nor any allocating routine is called.
+ */
+int xmc_large_k_matmul_noalloc(int32_t device, const void* a_bf16, const void* b, int32_t b_dtype,
+                               int32_t k, int32_t m, int32_t n, float* c_f32, void* stream);
+
+/*
  * Test hook (not used by the layer classes): D[M x N] fp32 = A * B^T on the library's GEMM
  * engine, to validate the tensor-core path in isolation.
  *   layout 0: A [M x K], B [N x K] both K-major (row-major as written), dtype XMC_DT_BF16 or XMC_DT_E4M3
