@@ -231,8 +231,16 @@ def run_ours(args, wl, rank, local_rank, world):
     cap = max(int(l.shape[0]) for _, l in pool) + 64
 
     if world == 1:
-        layer = Fp8XMCBCEChunkedLayer(layer_cfg(wl, device, b_loc, sched=args.sched))
-        fill_weights([p.data for p in layer.xfc_weight], wl.dim, seed=0)
+        if wl.mode == "bf16":
+            from elmo_b200.xmc_classifiers import XMCBCECHUNKEDLayer
+            layer = XMCBCECHUNKEDLayer(layer_cfg(wl, device, b_loc, sched=args.sched))
+            gen = torch.Generator().manual_seed(0)
+            for s0 in range(0, wl.num_labels, 65536):
+                blk = layer.xfc_weight[s0:s0 + 65536]
+                blk.copy_(synth.make_weights_f32(blk.shape[0], wl.dim, gen).to(torch.bfloat16))
+        else:
+            layer = Fp8XMCBCEChunkedLayer(layer_cfg(wl, device, b_loc, sched=args.sched))
+            fill_weights([p.data for p in layer.xfc_weight], wl.dim, seed=0)
         handle = layer._handle
         n_rows = layer.num_labels
         step_fn = lambda x, lab: layer.xfc_forward_backward(x, lab, [wl.lr], skip_loss=True)
@@ -280,6 +288,9 @@ def run_ours(args, wl, rank, local_rank, world):
     prof = handle.profile(False, read=True)
     peak_hbm = (torch.cuda.max_memory_allocated(device) + handle.workspace_bytes) / 1e9
 
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
     if rank != 0:
         return
     pk = peaks()

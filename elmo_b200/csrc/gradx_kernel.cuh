@@ -89,12 +89,12 @@ gradx_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant__ 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kGxStages; ++s) {
       mbar_init(smem_u32(&sh.a_full[s]), 1);
-      mbar_init(smem_u32(&sh.b_full[s]), CONVERT ? 32 * kGxWarps : 1);
+      mbar_init(smem_u32(&sh.b_full[s]), CONVERT ? kGxWarps : 1);
       mbar_init(smem_u32(&sh.mma_done[s]), 1);
     }
     for (int s = 0; s < kGxRawStages; ++s) {
       mbar_init(smem_u32(&sh.raw_full[s]), 1);
-      mbar_init(smem_u32(&sh.raw_empty[s]), 32 * kGxWarps);
+      mbar_init(smem_u32(&sh.raw_empty[s]), kGxWarps);
     }
     mbar_init(smem_u32(&sh.tmem_full), 1);
     sh.ctl.abort = 0;
@@ -166,7 +166,7 @@ gradx_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant__ 
     }
   } else {
     // -------------------- converters, then epilogue (warps 2..9) --------------------
-    const int cw = warp - 2, ct = cw * 32 + lane;                 // 0..255
+    const int cw = warp - 2;                                      // 0..7
     bool ok = true;
     if constexpr (CONVERT) {
       for (int i = 0; i < k_steps && ok; ++i) {
@@ -195,8 +195,11 @@ gradx_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant__ 
           *reinterpret_cast<uint4*>(rowp + (((2 * kc + 1) ^ (row & 7)) << 4)) = o1;
         }
         fence_proxy_async();                                      // generic-proxy writes -> tensor-core reads
-        mbar_arrive(smem_u32(&sh.b_full[s]));
-        mbar_arrive(smem_u32(&sh.raw_empty[rs]));
+        __syncwarp();                                             // one arrival per warp: 256 arrivals on one
+        if (lane == 0) {                                          // barrier word would serialise the stage
+          mbar_arrive(smem_u32(&sh.b_full[s]));
+          mbar_arrive(smem_u32(&sh.raw_empty[rs]));
+        }
       }
     }
     if (ok && mbar_wait(smem_u32(&sh.tmem_full), 0u, &sh.ctl, p.status, 560)) {
