@@ -10,7 +10,7 @@ import re
 from . import build as _build
 
 XMC_OK = 0
-DT_BF16, DT_E4M3, DT_F32 = 0, 1, 2
+DT_BF16, DT_E4M3, DT_F32, DT_E5M2 = 0, 1, 2, 3
 MODE_BF16, MODE_FP8, MODE_SIMFP8 = 0, 1, 2
 STEP_COMPUTE_LOSS, STEP_STOCHASTIC, STEP_ROUND_DW_BF16 = 1, 2, 4
 
@@ -31,6 +31,7 @@ _SIGNATURES = {
     "xmc_create": (C.c_int, [C.POINTER(XmcConfig), C.POINTER(C.c_void_p)]),
     "xmc_destroy": (C.c_int, [C.c_void_p]),
     "xmc_bind_weights": (C.c_int, [C.c_void_p, C.c_int32, C.POINTER(C.c_void_p), C.POINTER(C.c_int64)]),
+    "xmc_bind_kahan": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32]),
     "xmc_step": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int64,
                            C.c_float, C.c_float, C.c_uint64, C.c_uint64, C.c_uint32,
                            C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),

@@ -158,6 +158,9 @@ struct xmc_handle {
   int* status = nullptr;           // 4 ints
   int64_t ws_bytes = 0;
   // bookkeeping for the bench: kernels launched so far, optional per-kernel-class event timing
+  void* kahan = nullptr;           // borrowed compensation buffer for the first kahan_rows rows
+  int64_t kahan_rows = 0;
+  int kahan_e5m2 = 0;
   int64_t l2_persist_bytes = 0;    // size of the persisting-L2 carve-out this process asked for (0 = none)
   int64_t launches = 0;
   bool profile = false;
@@ -336,6 +339,24 @@ int xmc_bind_weights(xmc_handle* h, int32_t n_chunks, void* const* ptrs, const i
     h->loss_cap = (int64_t)n_chunks * spc * h->sm_count * xmc::kMaxEpiWarps;
     if (int rc = dev_alloc(h, (void**)&h->loss_partial, (size_t)h->loss_cap * 8, true)) return rc;
   }
+  return XMC_OK;
+}
+
+int xmc_bind_kahan(xmc_handle* h, void* buf, int64_t rows, int32_t dtype) {
+  if (h == nullptr) return fail(XMC_ERR_INVALID, "null handle");
+  if (buf == nullptr || rows == 0) {
+    h->kahan = nullptr;
+    h->kahan_rows = 0;
+    return XMC_OK;
+  }
+  if (h->cfg.mode != XMC_MODE_FP8) return fail(XMC_ERR_STATE, "the Kahan head is defined for the real-FP8 mode only");
+  if (h->w_ptrs.empty()) return fail(XMC_ERR_STATE, "bind the weights first");
+  if (dtype != XMC_DT_BF16 && dtype != XMC_DT_E5M2) return fail(XMC_ERR_INVALID, "compensation buffer must be bf16 or e5m2");
+  if (rows < 0 || rows > h->w_rows[0]) return fail(XMC_ERR_INVALID, "head rows %lld exceed the first weight chunk (%lld rows)", (long long)rows, (long long)h->w_rows[0]);
+  if ((uintptr_t)buf & 15u) return fail(XMC_ERR_INVALID, "compensation buffer not 16-byte aligned");
+  h->kahan = buf;
+  h->kahan_rows = rows;
+  h->kahan_e5m2 = dtype == XMC_DT_E5M2 ? 1 : 0;
   return XMC_OK;
 }
 
@@ -549,10 +570,22 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
       mark(h, K_UPD, st);
       // the reference pairs: e4m3 weights (no dW rounding), bf16 weights (dW materialised in bf16);
       // weight decay is off in both, so only those combinations get the branch-free fast kernels
+      up.kahan = nullptr;
+      up.kahan_rows = 0;
+      up.kahan_e5m2 = h->kahan_e5m2;
+      const bool kahan_here = h->kahan != nullptr && wc == 0 && s0 < h->kahan_rows;
+      if (kahan_here) {
+        if (!w8 || up.round_dw_bf16 || wd != 0.f) return fail(XMC_ERR_STATE, "the Kahan head needs e4m3 weights without weight decay");
+        up.kahan = reinterpret_cast<uint8_t*>(h->kahan) + (size_t)s0 * d * (h->kahan_e5m2 ? 1 : 2);
+        up.kahan_rows = (int)std::min<int64_t>(h->kahan_rows - s0, rows_valid);
+      }
       const bool rdw = up.round_dw_bf16 != 0, has_wd = wd != 0.f;
 #define XMC_UPD(W8_, SR_, RD_, WD_) \
   launch_gemm<xmc::UpdPolicy<W8_, SR_, RD_, WD_>>(map_g_k, map_xt, up, u_tiles, h->sm_count, st)
-      if (w8) {
+      if (kahan_here) {
+        rc = sr ? launch_gemm<xmc::UpdPolicy<true, true, false, false, true>>(map_g_k, map_xt, up, u_tiles, h->sm_count, st)
+                : launch_gemm<xmc::UpdPolicy<true, false, false, false, true>>(map_g_k, map_xt, up, u_tiles, h->sm_count, st);
+      } else if (w8) {
         if (!rdw && !has_wd) rc = sr ? XMC_UPD(true, true, false, false) : XMC_UPD(true, false, false, false);
         else if (!rdw) rc = sr ? XMC_UPD(true, true, false, true) : XMC_UPD(true, false, false, true);
         else rc = sr ? XMC_UPD(true, true, true, true) : XMC_UPD(true, false, true, true);

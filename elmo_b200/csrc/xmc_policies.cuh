@@ -178,10 +178,14 @@ struct UpdParams {
   unsigned long long seed, step;
   unsigned long long elem0;   // global flat element index of W[0][0] of this chunk (Philox counter origin)
   int round_dw_bf16;
+  // Kahan-compensated head rows (reference: fuse_kernel.py:202-287, chunked_head_kahan_fp8xmc_clf.py:127-131)
+  void* kahan;             // compensation rows of this chunk's row 0.., [kahan_rows x d] bf16 or e5m2; or nullptr
+  int kahan_rows;          // rows [0, kahan_rows) of this chunk are compensated
+  int kahan_e5m2;
   int* status;
 };
 
-template <bool W8, bool SR, bool ROUND_DW, bool HAS_WD>
+template <bool W8, bool SR, bool ROUND_DW, bool HAS_WD, bool KAHAN = false>
 struct UpdPolicy {
   using Params = UpdParams;
   static constexpr bool kMnMajor = false;
@@ -290,6 +294,78 @@ struct UpdPolicy {
     }
   }
 
+  // Kahan-compensated rows: w = W + D - lr*acc; W' = round(w); D' = cast(D + W - W' - lr*acc)
+  // (fuse_kernel.py:253-273).  Not on the fast path: only the head rows of chunk 0 come here.
+  __device__ static void process_w8_kahan(const Params& p, const uint32_t (&v)[32], const uint4 (&w16)[2],
+                                          unsigned long long elem, uint8_t* dst, void* krow, bool store_lo,
+                                          bool store_hi) {
+    uint32_t r[16];
+    if (SR) random32(p, elem, r);
+#pragma unroll 1
+    for (int h = 0; h < 2; ++h) {
+      if (!(h == 0 ? store_lo : store_hi)) continue;
+      float dv[16];
+      if (p.kahan_e5m2) {
+        const uint4 raw = reinterpret_cast<const uint4*>(krow)[h];
+        const uint32_t rk[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(rk[i >> 1] >> (16 * (i & 1))), __NV_E5M2);
+          const float2 f = __half22float2(*reinterpret_cast<__half2*>(&hr));
+          dv[2 * i] = f.x; dv[2 * i + 1] = f.y;
+        }
+      } else {
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+          const uint4 raw = reinterpret_cast<const uint4*>(krow)[2 * h + g];
+          const uint32_t rk[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            dv[8 * g + 2 * i] = bf16_bits_to_float(rk[i] & 0xFFFFu);
+            dv[8 * g + 2 * i + 1] = bf16_bits_to_float(rk[i] >> 16);
+          }
+        }
+      }
+      const uint32_t rw[4] = {w16[h].x, w16[h].y, w16[h].z, w16[h].w};
+      uint32_t ow[4];
+      float dn[16];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {          // pairs
+        const float2 f = e4m3x2_to_float2((uint16_t)(rw[k >> 1] >> (16 * (k & 1))));
+        const float wv[2] = {f.x, f.y};
+        float on[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int e = 16 * h + 2 * k + i;
+          const float a = __uint_as_float(v[e]);
+          float o = fmaf(-p.lr_eff, a, __fadd_rn(wv[i], dv[2 * k + i]));
+          if (SR) o = sr_e4m3(o, r16_of(r, e));
+          else o = e4m3x2_to_float2(float2_to_e4m3x2(o, 0.f)).x;       // the value W' will hold
+          on[i] = o;
+          dn[2 * k + i] = __fsub_rn(__fsub_rn(__fadd_rn(dv[2 * k + i], wv[i]), o), __fmul_rn(p.lr_eff, a));
+        }
+        const uint32_t pair = float2_to_e4m3x2(on[0], on[1]);
+        if (k & 1) ow[k >> 1] |= pair << 16; else ow[k >> 1] = pair;
+      }
+      *reinterpret_cast<uint4*>(dst + 16 * h) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+      if (p.kahan_e5m2) {
+        uint32_t ok[4];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const uint32_t pr = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(dn[2 * i], dn[2 * i + 1]), __NV_NOSAT, __NV_E5M2);
+          if (i & 1) ok[i >> 1] |= pr << 16; else ok[i >> 1] = pr;
+        }
+        reinterpret_cast<uint4*>(krow)[h] = make_uint4(ok[0], ok[1], ok[2], ok[3]);
+      } else {
+#pragma unroll
+        for (int g = 0; g < 2; ++g)
+          reinterpret_cast<uint4*>(krow)[2 * h + g] =
+              make_uint4(pack_bf16x2(dn[8 * g], dn[8 * g + 1]), pack_bf16x2(dn[8 * g + 2], dn[8 * g + 3]),
+                         pack_bf16x2(dn[8 * g + 4], dn[8 * g + 5]), pack_bf16x2(dn[8 * g + 6], dn[8 * g + 7]));
+      }
+    }
+  }
+
   __device__ static void process_bf16(const Params& p, const uint32_t (&v)[32], unsigned long long elem,
                                       __nv_bfloat16* wp, int valid16) {
     uint32_t r[16];
@@ -334,6 +410,13 @@ struct UpdPolicy {
           w16[h] = (row_valid && col + 16 * h < p.d) ? *reinterpret_cast<const uint4*>(wp + 16 * h)
                                                      : make_uint4(0, 0, 0, 0);
         load_acc(taddr + c0, have_acc, v);
+        if constexpr (KAHAN) {
+          if (row_valid && crow < p.kahan_rows) {
+            uint8_t* krow = reinterpret_cast<uint8_t*>(p.kahan) + ((size_t)crow * p.d + col) * (p.kahan_e5m2 ? 1 : 2);
+            process_w8_kahan(p, v, w16, erow + c0, wp, krow, col < p.d, col + 16 < p.d);
+            continue;
+          }
+        }
         if (row_valid) process_w8(p, v, w16, erow + c0, wp, col < p.d, col + 16 < p.d);
       } else {
         __nv_bfloat16* wp = reinterpret_cast<__nv_bfloat16*>(p.W) + (size_t)crow * p.d + col;

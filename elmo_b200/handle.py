@@ -77,6 +77,17 @@ class XmcHandle:
         self._keep = list(weights)
         self.total_rows = sum(int(w.shape[0]) for w in weights)
 
+    def bind_kahan(self, buf: Optional[torch.Tensor]):
+        """Attach (or with None detach) the compensation buffer of the Kahan head rows."""
+        if buf is None:
+            _lib.check(self.lib.xmc_bind_kahan(self._h, C.c_void_p(0), 0, _lib.DT_BF16))
+            self._kahan = None
+            return
+        assert buf.is_cuda and buf.is_contiguous() and buf.dim() == 2 and buf.shape[1] == self.dim
+        dt = {torch.bfloat16: _lib.DT_BF16, torch.float8_e5m2: _lib.DT_E5M2}[buf.dtype]
+        _lib.check(self.lib.xmc_bind_kahan(self._h, _ptr(buf), int(buf.shape[0]), dt))
+        self._kahan = buf
+
     def step(self, x: torch.Tensor, labels: Optional[torch.Tensor], lr: float, *, wd: float = 0.0,
              seed: int = 0, step: int = 0, stochastic: bool = True, compute_loss: bool = False,
              round_dw_bf16: bool = False, grad_f32: Optional[torch.Tensor] = None,

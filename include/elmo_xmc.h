@@ -40,7 +40,7 @@ enum {
 };
 
 /* element types */
-enum { XMC_DT_BF16 = 0, XMC_DT_E4M3 = 1, XMC_DT_F32 = 2 };
+enum { XMC_DT_BF16 = 0, XMC_DT_E4M3 = 1, XMC_DT_F32 = 2, XMC_DT_E5M2 = 3 };
 
 /* arithmetic of the forward contraction */
 enum {
@@ -84,6 +84,15 @@ int xmc_destroy(xmc_handle* h);
  * the concatenation of the chunks; row r of the concatenation has global id label_offset + r.
  */
 int xmc_bind_weights(xmc_handle* h, int32_t n_chunks, void* const* ptrs, const int64_t* rows);
+
+/*
+ * Kahan-compensated head (reference: src/xmc_classifiers/chunked_head_kahan_fp8xmc_clf.py:41-48,127-131,
+ * src/triton_kernels/fuse_kernel.py:202-287): the first `rows` label rows (<= rows of the first weight
+ * chunk) carry a compensation buffer D [rows x dim] (bf16 or e5m2, borrowed, updated in place):
+ *   w = W + D - lr*acc;  W' = round(w);  D' = cast(D + W - W' - lr*acc).
+ * Real-FP8 mode only; buf == NULL or rows == 0 removes it.
+ */
+int xmc_bind_kahan(xmc_handle* h, void* buf, int64_t rows, int32_t dtype);
 
 /*
  * One train step over all bound label rows:
