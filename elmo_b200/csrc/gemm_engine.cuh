@@ -192,7 +192,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       Policy::job(p, tile, job);
       const uint32_t buf = t_local & 1u, aph = (t_local >> 1) & 1u;
       Policy::epilogue_pre(p, job, sh, ec, st);          // overlaps the tile's main loop
-      if (!mbar_wait(smem_u32(&sh.tmem_full[buf]), aph, &sh.ctl, p.status, 400 + (int)buf)) break;
+      if (!mbar_wait_relaxed(smem_u32(&sh.tmem_full[buf]), aph, &sh.ctl, p.status, 400 + (int)buf)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * kTileN;
       Policy::epilogue(p, job, taddr, job.k_steps > 0, sh, ec, st);

@@ -202,7 +202,7 @@ gradx_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant__ 
         }
       }
     }
-    if (ok && mbar_wait(smem_u32(&sh.tmem_full), 0u, &sh.ctl, p.status, 560)) {
+    if (ok && mbar_wait_relaxed(smem_u32(&sh.tmem_full), 0u, &sh.ctl, p.status, 560)) {
       tc_fence_after();
       const int q = warp & 3;
       const int hm = cw >> 2;                                     // warps 2..5 -> accumulator 0, 6..9 -> 1
@@ -229,10 +229,15 @@ gradx_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant__ 
                                    __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
             float4* ptr = reinterpret_cast<float4*>(dstp + cg + 4 * i);
             if (p.accumulate) {
-              const float4 old = *ptr;
-              o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+              // Fire-and-forget vector reduction at L2: no read latency in the kernel's tail.  Each
+              // element has exactly one writer per launch and launches are stream-ordered, so the
+              // order of additions is still fixed.
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(ptr), "f"(o.x), "f"(o.y),
+                           "f"(o.z), "f"(o.w)
+                           : "memory");
+            } else {
+              *ptr = o;
             }
-            *ptr = o;
           }
         }
       }

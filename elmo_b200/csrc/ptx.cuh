@@ -97,6 +97,29 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Ctl* ct
   }
 }
 
+// Same, for waits that are expected to last a whole main loop (epilogue warps waiting for their
+// accumulator): back off with nanosleep so that the pollers do not compete for issue slots with the
+// producer and MMA-issuing warps.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, Ctl* ctl, int* status,
+                                                  int where) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (true) {
+    __nanosleep(spins < 16 ? 100 : 400);
+    if (mbar_try_wait(bar, parity)) return true;
+    ++spins;
+    if ((spins & 63u) == 0u) {
+      if (ctl->abort) return false;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        ctl->abort = 1;
+        report(status, DEV_WAIT_TIMEOUT, where);
+        return false;
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // TMA: 2-D tiled load, global -> shared, completion on an mbarrier (no multicast anywhere)
 // ---------------------------------------------------------------------------------------------
