@@ -76,13 +76,16 @@ __device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint2 k) {
 // trick, fuse_kernel.py:28-36).  Below 2^-6 the grid is uniform (step 2^-9): shift the value into
 // the binade [2^-6, 2^-5), whose 3-bit step is 2^-9, round there and shift back (both exact).
 __device__ __forceinline__ float sr_e4m3(float w, uint32_t r16) {
-  // branch-free: this runs for every weight element, interleaved across elements by the scheduler
-  const float a = fminf(fabsf(w), 448.0f);               // fminf drops a NaN operand; restored below
-  const float off = a < 0.015625f ? 0.015625f : 0.0f;
-  const uint32_t bits = (__float_as_uint(a + off) + (r16 << 4)) & 0xFFF00000u;
-  const float y = fminf(__uint_as_float(bits) - off, 448.0f);
-  const float out = copysignf(y, w);
-  return w != w ? w : out;
+  // Branch-free and light on the integer/compare pipe: this runs for every weight element.  The bit
+  // trick works on the signed value directly (adding to a sign-magnitude pattern grows the
+  // magnitude); the shift into the binade [2^-6, 2^-5) uses an offset carrying the sign of w.
+  // Values beyond +-448 and infinities are left to the saturating e4m3 conversion that follows; a
+  // result of zero is +0.
+  const uint32_t wb = __float_as_uint(w);
+  const float offs = __uint_as_float((fabsf(w) < 0.015625f ? 0x3C800000u : 0u) | (wb & 0x80000000u));
+  const uint32_t bits = (__float_as_uint(w + offs) + (r16 << 4)) & 0xFFF00000u;
+  const float y = __uint_as_float(bits) - offs;
+  return w != w ? w : y;
 }
 // Stochastic rounding onto the bf16 grid: add 16 random bits below the kept mantissa, truncate
 // (fuse_kernel.py:10-17).  Returns the bf16 bit pattern.
