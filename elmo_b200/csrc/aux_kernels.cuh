@@ -162,6 +162,72 @@ __global__ void reduce_gradx_kernel(const float* __restrict__ partial, int n_spl
   }
 }
 
+// Final top-k of one batch row from the candidate lists left by the top-k launches.  One block per
+// row; k rounds of "block-wide best remaining candidate" (value descending, then id ascending).
+// Candidate (launch l, CTA c, slot s, lane) belongs to row (c % n_mtiles)*128 + (s & 3 mapped to its
+// TMEM quarter)*32 + lane; list_of_row enumerates exactly those lists.
+__global__ void topk_merge_kernel(float* __restrict__ cand_val, int* __restrict__ cand_idx, int n_launch,
+                                  int grid, int n_mtiles, int k, int batch, long long label_offset,
+                                  float* __restrict__ out_val, int* __restrict__ out_idx) {
+  const int b = blockIdx.x;
+  if (b >= batch) return;
+  const int mt = b >> 7, q = (b >> 5) & 3, lane = b & 31;
+  const int ctas = grid / n_mtiles;                     // CTAs per batch tile in every launch
+  const int lists = n_launch * ctas * 2;                // two epilogue warps (column phases) per quarter
+  const long long total = (long long)lists * k;
+  __shared__ float s_val[32];
+  __shared__ long long s_pos[32];
+  __shared__ int s_id[32];
+  for (int round = 0; round < k; ++round) {
+    float best = -INFINITY;
+    long long best_pos = -1;
+    int best_id = 0x7fffffff;
+    for (long long t = threadIdx.x; t < total; t += blockDim.x) {
+      const int li = (int)(t / k), e = (int)(t - (long long)li * k);
+      const int l = li / (ctas * 2), r = li - l * ctas * 2;
+      const int c = (r >> 1) * n_mtiles + mt, ph = r & 1;
+      // epilogue warp slots 0..7 are warps 2..9; warp w owns quarter w & 3: slot -> quarter (slot + 2) & 3
+      int slot = -1;
+      for (int sl = 4 * ph; sl < 4 * ph + 4; ++sl)
+        if (((sl + 2) & 3) == q) slot = sl;
+      const long long pos = ((((long long)l * grid + c) * 8 + slot) * 32 + lane) * k + e;
+      const float v = cand_val[pos];
+      const int id = cand_idx[pos];
+      if (id >= 0 && (v > best || (v == best && id < best_id))) {
+        best = v; best_pos = pos; best_id = id;
+      }
+    }
+    // block reduction
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const long long op = __shfl_xor_sync(0xffffffffu, best_pos, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_id, o);
+      if (op >= 0 && (best_pos < 0 || ov > best || (ov == best && oi < best_id))) { best = ov; best_pos = op; best_id = oi; }
+    }
+    const int w = threadIdx.x >> 5, ln = threadIdx.x & 31;
+    if (ln == 0) { s_val[w] = best; s_pos[w] = best_pos; s_id[w] = best_id; }
+    __syncthreads();
+    if (w == 0) {
+      const int nw = blockDim.x >> 5;
+      best = ln < nw ? s_val[ln] : -INFINITY;
+      best_pos = ln < nw ? s_pos[ln] : -1;
+      best_id = ln < nw ? s_id[ln] : 0x7fffffff;
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const long long op = __shfl_xor_sync(0xffffffffu, best_pos, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_id, o);
+        if (op >= 0 && (best_pos < 0 || ov > best || (ov == best && oi < best_id))) { best = ov; best_pos = op; best_id = oi; }
+      }
+      if (ln == 0) {
+        out_val[(size_t)b * k + round] = best_pos >= 0 ? best : -INFINITY;
+        out_idx[(size_t)b * k + round] = best_pos >= 0 ? (int)(label_offset + best_id) : -1;
+        if (best_pos >= 0) cand_idx[best_pos] = -1;                       // consumed
+      }
+    }
+    __syncthreads();
+  }
+}
+
 // loss = sum of n partials in index order, one thread (n is a few thousand at most)
 __global__ void reduce_loss_kernel(const double* __restrict__ partial, int n, double* __restrict__ out) {
   if (blockIdx.x == 0 && threadIdx.x == 0) {

@@ -115,12 +115,12 @@ int make_map_mnmajor(CUtensorMap* m, const void* base, uint64_t mn, uint64_t k_r
 
 template <class Policy>
 int launch_gemm(const CUtensorMap& a, const CUtensorMap& b, const typename Policy::Params& p, int n_tiles,
-                int sm_count, cudaStream_t stream) {
+                int sm_count, cudaStream_t stream, int grid_override = 0) {
   if (n_tiles <= 0) return XMC_OK;
   auto kern = xmc::gemm_kernel<Policy>;
   // per device and cheap; one process may drive several devices
   CU_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, xmc::kSmemBytes));
-  const int grid = std::min(n_tiles, sm_count);
+  const int grid = grid_override > 0 ? grid_override : std::min(n_tiles, sm_count);
   kern<<<grid, 64 + 32 * Policy::kEpiWarps, xmc::kSmemBytes, stream>>>(a, b, p);
   CU_TRY(cudaGetLastError());
   return XMC_OK;
@@ -158,6 +158,9 @@ struct xmc_handle {
   int* status = nullptr;           // 4 ints
   int64_t ws_bytes = 0;
   // bookkeeping for the bench: kernels launched so far, optional per-kernel-class event timing
+  float* topk_val = nullptr;       // candidate lists of the fused top-k (grown on demand)
+  int* topk_idx = nullptr;
+  int64_t topk_cap = 0;            // entries
   void* kahan = nullptr;           // borrowed compensation buffer for the first kahan_rows rows
   int64_t kahan_rows = 0;
   int kahan_e5m2 = 0;
@@ -301,7 +304,7 @@ int xmc_destroy(xmc_handle* h) {
   if (h == nullptr) return XMC_OK;
   DeviceGuard guard(h->cfg.device);
   void* ptrs[] = {h->x8, h->x16, h->xt, h->G, h->w16, h->partial, h->bucket_cnt, h->bucket_off,
-                  h->entries, h->loss_partial, h->status};
+                  h->entries, h->loss_partial, h->status, h->topk_val, h->topk_idx};
   for (void* p : ptrs)
     if (p != nullptr) cudaFree(p);
   for (cudaEvent_t e : h->ev_pool) cudaEventDestroy(e);
@@ -704,8 +707,95 @@ int xmc_forward_logits(xmc_handle* h, const void* x, int32_t x_dtype, int32_t ba
   mark(h, K_END, st);
   return XMC_OK;
 }
-int xmc_forward_topk(xmc_handle*, const void*, int32_t, int32_t, int32_t, int64_t, float*, int32_t*, void*) {
-  return fail(XMC_ERR_STATE, "xmc_forward_topk: not built yet");
+int xmc_forward_topk(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, int32_t k, int64_t n_out,
+                     float* vals, int32_t* idx, void* stream) {
+  if (h == nullptr || x == nullptr || vals == nullptr || idx == nullptr) return fail(XMC_ERR_INVALID, "null argument");
+  if (h->w_ptrs.empty()) return fail(XMC_ERR_STATE, "xmc_bind_weights has not been called");
+  if (x_dtype != XMC_DT_BF16 && x_dtype != XMC_DT_E4M3) return fail(XMC_ERR_INVALID, "embeddings must be bf16 or e4m3");
+  if (batch <= 0 || batch > h->cfg.max_batch) return fail(XMC_ERR_INVALID, "batch %d outside [1, %d]", batch, h->cfg.max_batch);
+  if (k <= 0 || k > 128) return fail(XMC_ERR_INVALID, "k must be in [1, 128], got %d", k);
+  if (n_out <= 0 || n_out > h->total_rows) return fail(XMC_ERR_INVALID, "n_out %lld outside [1, %lld]", (long long)n_out, (long long)h->total_rows);
+  DeviceGuard guard(h->cfg.device);
+  cudaStream_t st = (cudaStream_t)stream;
+  const int d = h->cfg.dim, mode = h->cfg.mode;
+  const int bpad = (int)round_up(batch, 64);
+  const bool fwd_fp8 = mode == XMC_MODE_FP8;
+  const int n_mt = cdiv(batch, 128);
+  if (n_mt > h->sm_count) return fail(XMC_ERR_INVALID, "batch too large for the fused top-k");
+  const int grid_max = h->sm_count / n_mt * n_mt;
+  const int spc = cdiv(h->rows_per_chunk, h->sched);
+  const int n_launch_max = (int)h->w_ptrs.size() * spc;
+  const int64_t need = (int64_t)n_launch_max * grid_max * 256 * k;
+  if (need > h->topk_cap) {
+    CU_TRY(cudaStreamSynchronize(st));
+    if (h->topk_val) { cudaFree(h->topk_val); cudaFree(h->topk_idx); h->ws_bytes -= h->topk_cap * 8; h->topk_val = nullptr; h->topk_idx = nullptr; }
+    h->topk_cap = 0;
+    if (int rc = dev_alloc(h, (void**)&h->topk_val, (size_t)need * 4, false)) return rc;
+    if (int rc = dev_alloc(h, (void**)&h->topk_idx, (size_t)need * 4, false)) return rc;
+    h->topk_cap = need;
+  }
+  CU_TRY(cudaMemsetAsync(h->topk_idx, 0xFF, (size_t)need * 4, st));      // id -1: "no candidate"
+  if (int rc = prep_x(h, x, x_dtype, batch, bpad, fwd_fp8, !fwd_fp8, false, st)) return rc;
+  CUtensorMap map_x;
+  const size_t xrows = (size_t)std::max(h->bpad_max, 256);
+  if (fwd_fp8) {
+    if (int rc = make_map_kmajor(&map_x, true, h->x8, d, xrows, d, 128)) return rc;
+  } else {
+    if (int rc = make_map_kmajor(&map_x, false, h->x16, d, xrows, d, 128)) return rc;
+  }
+  int launch = 0;
+  int64_t row_base = 0;
+  for (size_t wc = 0; wc < h->w_ptrs.size() && row_base < n_out; ++wc) {
+    const int64_t rows_wc = h->w_rows[wc];
+    for (int64_t s0 = 0; s0 < rows_wc && row_base + s0 < n_out; s0 += h->sched) {
+      const int rows = (int)std::min<int64_t>(h->sched, rows_wc - s0);
+      const size_t esz = mode == XMC_MODE_BF16 ? 2 : 1;
+      const uint8_t* wbase = reinterpret_cast<const uint8_t*>(h->w_ptrs[wc]) + (size_t)s0 * d * esz;
+      const void* wsrc = wbase;
+      if (mode == XMC_MODE_SIMFP8) {
+        const long long n16 = (long long)rows * d / 16;
+        const int blocks = (int)std::min<long long>((n16 + 255) / 256, (long long)h->sm_count * 8);
+        mark(h, K_CONVERT, st);
+        xmc::e4m3_to_bf16_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const uint4*>(wbase),
+                                                         reinterpret_cast<uint4*>(h->w16), n16);
+        CU_TRY(cudaGetLastError());
+        wsrc = h->w16;
+      }
+      CUtensorMap map_w;
+      if (int rc = make_map_kmajor(&map_w, fwd_fp8, wsrc, d, rows, d, 256)) return rc;
+      xmc::TopkParams tp;
+      tp.batch = batch;
+      tp.rows = rows;
+      tp.n_mtiles = n_mt;
+      tp.n_ntiles = cdiv(rows, 256);
+      tp.k_steps = cdiv((long long)d * (fwd_fp8 ? 1 : 2), 128);
+      tp.k = k;
+      tp.w_scale = h->cfg.w_scale;
+      tp.col0 = row_base + s0;
+      tp.n_out = n_out;
+      tp.cand_val = h->topk_val + (size_t)launch * grid_max * 256 * k;
+      tp.cand_idx = h->topk_idx + (size_t)launch * grid_max * 256 * k;
+      tp.status = h->status;
+      const int tiles = tp.n_mtiles * tp.n_ntiles;
+      const int grid = std::min(tiles, grid_max) / n_mt * n_mt;
+      mark(h, K_LOGITS, st);
+      int rc;
+#define XMC_TOPK(F8_, KM_) launch_gemm<xmc::TopkPolicy<F8_, KM_>>(map_x, map_w, tp, tiles, h->sm_count, st, grid)
+      if (k <= 8) rc = fwd_fp8 ? XMC_TOPK(true, 8) : XMC_TOPK(false, 8);
+      else if (k <= 32) rc = fwd_fp8 ? XMC_TOPK(true, 32) : XMC_TOPK(false, 32);
+      else rc = fwd_fp8 ? XMC_TOPK(true, 128) : XMC_TOPK(false, 128);
+#undef XMC_TOPK
+      if (rc) return rc;
+      ++launch;
+    }
+    row_base += rows_wc;
+  }
+  mark(h, K_LOGITS, st);
+  xmc::topk_merge_kernel<<<batch, 256, 0, st>>>(h->topk_val, h->topk_idx, launch, grid_max, n_mt, k, batch,
+                                                h->cfg.label_offset, vals, idx);
+  CU_TRY(cudaGetLastError());
+  mark(h, K_END, st);
+  return XMC_OK;
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -499,6 +499,98 @@ struct LogitsPolicy {
 };
 
 // -------------------------------------------------------------------------------------------------
+// Fused logits + top-k (reference: evaluate.py:158-159 xfc_forward followed by torch.topk; the
+// logits are never stored).  Same contraction as LogitsPolicy; every epilogue thread keeps the k
+// best (bf16-rounded logit, label) pairs of ITS batch row over all label tiles its CTA visits, and
+// writes them out once at the end; a merge kernel picks the final k per row.  A CTA's batch tile is
+// fixed (the grid is a multiple of n_mtiles), so a thread's row never changes within a launch.
+// -------------------------------------------------------------------------------------------------
+struct TopkParams {
+  int batch, rows;
+  int n_mtiles, n_ntiles;
+  int k_steps;
+  int k;
+  float w_scale;
+  long long col0;          // index (within the handle) of this launch's label row 0
+  long long n_out;         // rows >= n_out are ignored (padding)
+  float* cand_val;         // [gridDim.x * 256 threads][k]
+  int* cand_idx;
+  int* status;
+};
+
+template <bool FP8, int KMAX>
+struct TopkPolicy {
+  using Params = TopkParams;
+  static constexpr bool kMnMajor = false;
+  static constexpr bool kFp8 = FP8;
+  static constexpr uint32_t kFmt = FP8 ? 0u : 1u;
+  static constexpr int kElemsPerRow = FP8 ? 128 : 64;
+  static constexpr int kEpiWarps = 8;
+  struct EpilogueState {
+    float val[KMAX];       // descending
+    int idx[KMAX];
+    float thr;             // val[k-1]
+  };
+  __device__ static int num_tiles(const Params& p) { return p.n_mtiles * p.n_ntiles; }
+  __device__ static void job(const Params& p, int tile, Job& j) {
+    j.t1 = tile / p.n_mtiles;
+    j.t0 = tile - j.t1 * p.n_mtiles;
+    j.a0 = j.t0 * kTileM;
+    j.b0 = j.t1 * kTileN;
+    j.k_begin = 0;
+    j.k_steps = p.k_steps;
+    j.n_eff = min(kTileN, round_up16(p.rows - j.b0));
+  }
+  __device__ static void epilogue_begin(const Params& p, EpilogueState& st) {
+    for (int i = 0; i < p.k; ++i) {
+      st.val[i] = -INFINITY;
+      st.idx[i] = -1;
+    }
+    st.thr = -INFINITY;
+  }
+  __device__ static void epilogue_pre(const Params&, const Job&, SharedTail&, const EpiCtx&, EpilogueState&) {}
+  __device__ static void epilogue(const Params& p, const Job& j, uint32_t taddr, bool have_acc,
+                                  SharedTail&, const EpiCtx& ec, EpilogueState& st) {
+    const int b = j.a0 + ec.q * 32 + ec.lane;
+    for (int c0 = 32 * ec.h; c0 < j.n_eff; c0 += 32 * ec.nsplit) {
+      uint32_t v[32];
+      if (have_acc) {
+        tmem_ld32(taddr + c0, v);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = 0u;
+      }
+      if (b >= p.batch) continue;
+      const long long col = p.col0 + j.b0 + c0;
+      const int valid = (int)max(0ll, min(32ll, min((long long)(p.rows - j.b0 - c0), p.n_out - col)));
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const float z = bf16_round(__uint_as_float(v[i]) * p.w_scale);
+        if (i < valid && z > st.thr) {            // labels arrive in ascending order: ties keep the lower id
+          int pos = p.k - 1;
+          while (pos > 0 && st.val[pos - 1] < z) {
+            st.val[pos] = st.val[pos - 1];
+            st.idx[pos] = st.idx[pos - 1];
+            --pos;
+          }
+          st.val[pos] = z;
+          st.idx[pos] = (int)(col + i);
+          st.thr = st.val[p.k - 1];
+        }
+      }
+    }
+  }
+  __device__ static void epilogue_end(const Params& p, SharedTail&, const EpiCtx& ec, EpilogueState& st) {
+    const size_t base = ((size_t)blockIdx.x * (kEpiWarps * 32) + ec.slot * 32 + ec.lane) * p.k;
+    for (int i = 0; i < p.k; ++i) {
+      p.cand_val[base + i] = st.val[i];
+      p.cand_idx[base + i] = st.idx[i];
+    }
+  }
+};
+
+// -------------------------------------------------------------------------------------------------
 // Plain D = A B^T, fp32 out (engine self-test; also the logits kernel's skeleton)
 // -------------------------------------------------------------------------------------------------
 struct PlainParams {

@@ -59,6 +59,11 @@ class CudaShardEngine:
         self.handle.step(x, labels, lr, seed=seed, step=step, stochastic=stochastic,
                          compute_loss=compute_loss, grad_f32=grad_f32, loss_out=loss_out)
 
+    def topk(self, x, k, n_out):
+        """(values fp32 [B, k], GLOBAL label ids int32 [B, k]) over this shard's first n_out rows."""
+        self.handle.bind(self.weights)
+        return self.handle.forward_topk(x, k, n_out)
+
 
 class LabelShardedXMC:
     """One rank's view of a label-sharded FP8 XMC layer.
@@ -96,6 +101,38 @@ class LabelShardedXMC:
         dist.all_gather_into_tensor(self._xg, x, group=self.group)
         dist.all_gather_into_tensor(self._lg, lab, group=self.group)
         return self._xg, self._lg
+
+    @torch.no_grad()
+    def xfc_topk(self, embed_local, k: int, num_labels: int):
+        """Top-k labels of the rank's own batch rows over ALL shards: every rank scores the gathered
+        batch against its label range (fused logits + top-k, nothing materialised), the per-shard
+        candidates [B, k] are all-gathered and merged locally.  ``num_labels`` is the true label count
+        (padding rows beyond it never appear).  Returns (values [B_loc, k], ids [B_loc, k])."""
+        x, _ = self.gather_inputs(embed_local, None)
+        lo, hi = self.bounds[self.rank]
+        n_out = max(0, min(hi, num_labels) - lo)
+        B = x.shape[0]
+        if n_out > 0:
+            vals, idx = self.engine.topk(x, min(k, n_out), n_out)
+            if vals.shape[1] < k:
+                pad = k - vals.shape[1]
+                vals = torch.cat([vals, vals.new_full((B, pad), float("-inf"))], 1)
+                idx = torch.cat([idx, idx.new_full((B, pad), -1)], 1)
+        else:
+            vals = torch.full((B, k), float("-inf"), dtype=torch.float32, device=self.device)
+            idx = torch.full((B, k), -1, dtype=torch.int32, device=self.device)
+        if self.world > 1:
+            all_v = torch.empty(self.world * B, k, dtype=vals.dtype, device=self.device)
+            all_i = torch.empty(self.world * B, k, dtype=idx.dtype, device=self.device)
+            dist.all_gather_into_tensor(all_v, vals.contiguous(), group=self.group)
+            dist.all_gather_into_tensor(all_i, idx.contiguous(), group=self.group)
+            cand_v = all_v.view(self.world, B, k).permute(1, 0, 2).reshape(B, self.world * k)
+            cand_i = all_i.view(self.world, B, k).permute(1, 0, 2).reshape(B, self.world * k)
+            # shards are in ascending label order, so a stable descending sort keeps the lower id on ties
+            order = torch.argsort(cand_v, dim=1, descending=True, stable=True)[:, :k]
+            vals, idx = torch.gather(cand_v, 1, order), torch.gather(cand_i, 1, order)
+        r0 = self.rank * self.local_batch
+        return vals[r0:r0 + self.local_batch], idx[r0:r0 + self.local_batch]
 
     def xfc_forward_backward(self, embed_local, labels_local, xmc_lr, skip_loss=True):
         x, lab = self.gather_inputs(embed_local, labels_local)

@@ -25,6 +25,11 @@ class OracleEngine:
             w.copy_(n)
         grad_f32.copy_(gx)
 
+    def topk(self, x, k, n_out):
+        from oracle import xmc_oracle as O
+        v, i = O.topk_logits([w[:n_out] for w in self.weights], x, k)
+        return v, (i + self.label_offset).to(torch.int32)
+
 
 def _data():
     g = torch.Generator().manual_seed(0)
@@ -49,7 +54,8 @@ def _worker(rank, port, out):
                                 label_capacity=16, base_seed=9, rounding="sr")
         for it in range(2):
             layer.xfc_forward_backward(xs[rank], labs[rank], [0.5])
-        out[rank] = (mine[0].view(torch.uint8).clone(), layer.grad_input.float().clone())
+        tv, ti = layer.xfc_topk(xs[rank], 4, L - 7)
+        out[rank] = (mine[0].view(torch.uint8).clone(), layer.grad_input.float().clone(), tv.clone(), ti.clone())
     finally:
         dist.destroy_process_group()
 
@@ -68,10 +74,13 @@ def test_two_rank_sharded_step_equals_unsharded():
         chunks, gx, _ = O.fp8_chunked_step(chunks, x, lab, 0.5, rounding="sr", seed=9, step=it)
     full = chunks[0].view(torch.uint8)
     for r, (lo, hi) in enumerate(shard_bounds(L, WORLD)):
-        w_r, g_r = out[r]
+        w_r, g_r, tv, ti = out[r]
         assert torch.equal(w_r, full[lo:hi])
         want = gx[r * B_LOC:(r + 1) * B_LOC].to(torch.bfloat16).float()
         assert torch.allclose(g_r, want, rtol=2e-2, atol=1e-6)
+        # sharded top-k (after the two steps) == top-k of the unsharded updated weights
+        wv, wi = O.topk_logits([chunks[0][:L - 7]], xs[r], 4)
+        assert torch.equal(tv, wv) and torch.equal(ti.long(), wi.long())
 
 
 def test_pad_labels_and_bounds():
