@@ -44,6 +44,17 @@ class XMCBCECHUNKEDLayer(nn.Module):
                                  label_offset=cfg_get(cfg, 'model.xmc.label_offset', 0),
                                  sched_labels=cfg_get(cfg, 'model.xmc.sched_labels', 0))
 
+    # ``xfc_weight`` is a plain attribute as in the reference (saved separately by runner.py:246); the
+    # stochastic-rounding stream position rides along in state_dict as extra state
+    def get_extra_state(self):
+        return {"base_seed": self.base_seed, "iteration": self.iteration, "rounding": self.rounding}
+
+    def set_extra_state(self, state):
+        if state:
+            self.base_seed = int(state.get("base_seed", self.base_seed))
+            self.iteration = int(state.get("iteration", self.iteration))
+            self.rounding = state.get("rounding", self.rounding)
+
     @torch.no_grad()
     def xfc_forward(self, embed):
         """Logits [B, num_labels] (chunked.py:48-53)."""

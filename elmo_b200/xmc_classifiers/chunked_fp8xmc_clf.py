@@ -87,6 +87,21 @@ class Fp8XMCBCEChunkedLayer(nn.Module):
         self.grad_input = self._grad_buf[:bsz]
         return 0 if skip_loss else float(self._loss_dev.item())
 
+    # --- checkpoint: the weights travel in state_dict as in the reference (runner.py:242-251); what the
+    # reference has no slot for (scale, stochastic-rounding stream position) rides along as extra state
+    def get_extra_state(self):
+        return {"w_scale": self.w_scale, "base_seed": self.base_seed, "iteration": self.iteration,
+                "rounding": self.rounding}
+
+    def set_extra_state(self, state):
+        if not state:
+            return
+        if float(state.get("w_scale", self.w_scale)) != self.w_scale:
+            raise ValueError(f"checkpoint was written with w_scale={state['w_scale']}, layer has {self.w_scale}")
+        self.base_seed = int(state.get("base_seed", self.base_seed))
+        self.iteration = int(state.get("iteration", self.iteration))
+        self.rounding = state.get("rounding", self.rounding)
+
     def filter_non_local_inds(self, rows, cols, start, end):
         mask = (cols >= start) & (cols < end)                                          # :124-126
         return rows[mask], cols[mask] - start

@@ -12,12 +12,16 @@ class Fp8XMCBCEChunkedHeadKahanLayer(Fp8XMCBCEChunkedLayer):
     def __init__(self, cfg):
         super().__init__(cfg)
         self.using_head_kahan = cfg.training.FP8.using_head_kahan
-        self.head_kahan = None
+        if not self.using_head_kahan:
+            self.head_kahan = None
         if self.using_head_kahan:
             self.fp8_head_kahan = cfg.training.FP8.fp8_head_kahan
             self.num_head = int(cfg.training.FP8.head_ratio * self.num_labels)        # :42
             dt = torch.float8_e5m2 if self.fp8_head_kahan else torch.bfloat16         # :43-46
-            self.head_kahan = torch.zeros(self.num_head, self.input_features, dtype=dt, device=self.device)
+            # a registered buffer, so that it is checkpointed with the weights (the reference keeps it
+            # as a plain attribute and loses it on save/load)
+            self.register_buffer("head_kahan", torch.zeros(self.num_head, self.input_features, dtype=dt,
+                                                           device=self.device))
             assert self.num_head <= self.num_labels_i                                 # :47
         self._kahan_ptr = None
 

@@ -100,5 +100,37 @@ def test_layer_step_through_class_api_matches_oracle():
         assert (p.data.cpu().view(torch.uint8) == w.view(torch.uint8)).float().mean() >= 0.999
     assert layer.iteration == 2
     sd = layer.state_dict()
-    assert sorted(sd) == [f"xfc_weight.{i}" for i in range(nc)]
+    assert sorted(k for k in sd if k != "_extra_state") == [f"xfc_weight.{i}" for i in range(nc)]
     layer._handle.check()
+
+
+def test_checkpoint_round_trip_continues_the_same_stochastic_stream():
+    """runner.py:242-268: state_dict save / load; a restored layer must take the same next step."""
+    import io
+    from elmo_b200.xmc_classifiers import Fp8XMCBCEChunkedHeadKahanLayer
+    L, d, B, nc = 2000, 128, 32, 2
+    cfg = _cfg(L, d, B, nc)
+    cfg.training.FP8 = NS(using_head_kahan=True, fp8_head_kahan=False, head_ratio=0.1)
+    torch.manual_seed(1)
+    a = Fp8XMCBCEChunkedHeadKahanLayer(cfg)
+    gen = torch.Generator().manual_seed(5)
+    for p in a.xfc_weight:
+        p.data.copy_((torch.randn(p.shape, generator=gen) * 0.25).to(torch.float8_e4m3fn))
+    x = (torch.randn(B, d, generator=gen) / d ** 0.5).to(torch.bfloat16).cuda()
+    lab = torch.stack([torch.randint(0, B, (100,), generator=gen),
+                       torch.randint(0, L, (100,), generator=gen)], 1).to(torch.int32).cuda()
+    a.xfc_forward_backward(x, lab, [0.5])
+    buf = io.BytesIO()
+    torch.save(a.state_dict(), buf)
+    buf.seek(0)
+    torch.manual_seed(999)                                   # a different construction-time seed
+    b = Fp8XMCBCEChunkedHeadKahanLayer(cfg)
+    b.load_state_dict(torch.load(buf))
+    assert b.iteration == 1 and b.base_seed == a.base_seed
+    assert torch.equal(b.head_kahan.view(torch.int16), a.head_kahan.view(torch.int16))
+    a.xfc_forward_backward(x, lab, [0.5])
+    b.xfc_forward_backward(x, lab, [0.5])
+    for pa, pb in zip(a.xfc_weight, b.xfc_weight):
+        assert torch.equal(pa.data.view(torch.uint8), pb.data.view(torch.uint8))
+    assert torch.equal(a.grad_input, b.grad_input)
+    a._handle.check(); b._handle.check()
