@@ -301,6 +301,12 @@ def run_ours(args, wl, rank, local_rank, world):
     dom_ms = per_step[dominant]
     dom_launches = prof[dominant][1] / n_prof
     achieved = gemm_flops / (dom_ms * 1e-3) / 1e12
+    # DRAM bytes per label row of one launch (dram__bytes_read.sum + dram__bytes_write.sum of an ncu
+    # capture of a 65 536-row chunk at batch 512, d 768: profiles/step_kernels_small_case.md); traffic
+    # grows with the rows a launch processes, so it is scaled to this run's rows per launch
+    dram_per_row = {"update": 130.6e6 / 65536, "grad_x": 160.1e6 / 65536, "forward": 65.4e6 / 65536}
+    rows_per_launch = (L / world) / max(dom_launches, 1.0)
+    traffic = dram_per_row[dominant] * rows_per_launch if (wl.dim == 768 and b_loc * world == 512) else None
     fp8_dom = dominant == "forward" and wl.mode == "fp8"
     peak = pk["bf16_sustained"] * (2.0 if fp8_dom else 1.0)
     step_ms = ms / args.steps
@@ -323,7 +329,8 @@ def run_ours(args, wl, rank, local_rank, world):
                 "d2h_bytes_per_step": int(host_grad.numel() * 2)},
         "gpu_launches": int(launches),
         "roofline": {"bound": "tensor", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                     "frac": achieved / peak, "traffic": None,
+                     "frac": achieved / peak, "traffic": traffic,
+                     "traffic_note": "DRAM bytes per launch, ncu capture of a 65536-row chunk scaled by rows per launch",
                      "peak_source": pk["source"] + (" bf16 sustained x2 (no measured fp8 figure)" if fp8_dom
                                                     else " bf16 sustained"),
                      "launches_per_step": dom_launches, "ms_per_step": dom_ms},
