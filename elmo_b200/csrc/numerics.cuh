@@ -11,13 +11,6 @@ namespace xmc {
 __device__ __forceinline__ float bf16_round(float x) {
   return __bfloat162float(__float2bfloat16_rn(x));
 }
-// Same rounding (nearest-even, NaN kept quiet) with integer ALU ops only: float<->bf16 cvt
-// instructions share the special-function pipe with ex2/rcp, which the forward epilogue saturates.
-__device__ __forceinline__ float bf16_round_alu(float x) {
-  const uint32_t u = __float_as_uint(x);
-  const uint32_t r = (u + 0x7FFFu + ((u >> 16) & 1u)) & 0xFFFF0000u;
-  return __uint_as_float((u & 0x7FFFFFFFu) > 0x7F800000u ? (u | 0x00400000u) & 0xFFFF0000u : r);
-}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -41,11 +34,6 @@ __device__ __forceinline__ float fast_sigmoid(float z) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(z * -1.4426950408889634f));
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
   return r;
-}
-// sigmoid of a bf16-valued float, rounded back to bf16 (the reference applies torch.sigmoid in
-// place on bf16 logits: chunked.py:112, chunked_fp8xmc_clf.py:107)
-__device__ __forceinline__ float sigmoid_bf16(float z) {
-  return bf16_round(__fdividef(1.0f, 1.0f + __expf(-z)));
 }
 // max(z,0) + log(1 + exp(-|z|)): the label-independent part of BCE-with-logits (chunked.py:57-72)
 __device__ __forceinline__ float bce_softplus(float z) {
