@@ -51,9 +51,11 @@ struct SharedTail {
   uint32_t tmem_base;
   Ctl ctl;
   uint32_t bitmap[kTileM * (kTileN / 32)];   // positives of one (label tile, batch tile)
+  alignas(16) uint8_t stage[8 * 2048];       // per-warp store staging (epilogues with up to 8 warps)
 };
 
 constexpr int kSmemBytes = kStages * kStageBytes + (int)sizeof(SharedTail) + 1024;
+static_assert(kSmemBytes <= 232448, "exceeds the 227 KB of shared memory a CTA can get");
 
 template <class Policy>
 __global__ void __launch_bounds__(64 + 32 * Policy::kEpiWarps, 1)

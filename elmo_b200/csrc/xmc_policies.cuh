@@ -44,6 +44,7 @@ struct FwdPolicy {
 #define XMC_FWD_WARPS 8
 #endif
   static constexpr int kEpiWarps = XMC_FWD_WARPS;
+  static_assert(kEpiWarps <= 8, "the store staging buffer holds 8 warps");
   struct EpilogueState {
     float loss;
     int has_pos;
@@ -89,7 +90,6 @@ struct FwdPolicy {
     const int row = ec.q * 32 + ec.lane;
     const int crow = j.a0 + row;
     const bool row_valid = crow < p.rows_valid;
-    __nv_bfloat16* grow = p.G + (size_t)crow * p.bpad + j.b0;
     for (int c0 = 32 * ec.h; c0 < j.n_eff; c0 += 32 * ec.nsplit) {
       uint32_t v[32];
       if (have_acc) {
@@ -146,12 +146,26 @@ struct FwdPolicy {
           else if (b + 1 >= p.batch) out[i] &= 0x0000FFFFu;
         }
       }
+      // Store through a per-warp 2 KB staging buffer so that every store instruction writes whole
+      // 64-byte runs of a row (4 lanes per row) instead of 32 scattered 16-byte pieces: lane = row
+      // writes its 64 B into shared memory (16-byte slots XOR-swizzled by row so that neither phase
+      // has bank conflicts), then lane L re-reads slot (L & 3) of row 8*i + (L >> 2).
+      uint8_t* stg = sh.stage + ec.slot * 2048;
+      const int lr = ec.lane;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        *reinterpret_cast<uint4*>(stg + lr * 64 + ((c ^ ((lr >> 1) & 3)) << 4)) =
+            make_uint4(out[4 * c], out[4 * c + 1], out[4 * c + 2], out[4 * c + 3]);
+      __syncwarp();
+      const int tile_row0 = j.a0 + ec.q * 32;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        if (j.b0 + c0 + 8 * i < p.bpad)
-          *reinterpret_cast<uint4*>(grow + c0 + 8 * i) =
-              make_uint4(out[4 * i], out[4 * i + 1], out[4 * i + 2], out[4 * i + 3]);
+        const int r = 8 * i + (lr >> 2), c = lr & 3;
+        const uint4 val = *reinterpret_cast<const uint4*>(stg + r * 64 + ((c ^ ((r >> 1) & 3)) << 4));
+        if (j.b0 + c0 + 8 * c < p.bpad)
+          *reinterpret_cast<uint4*>(p.G + (size_t)(tile_row0 + r) * p.bpad + j.b0 + c0 + 8 * c) = val;
       }
+      __syncwarp();
     }
   }
   __device__ static void epilogue_end(const Params& p, SharedTail&, const EpiCtx& ec, EpilogueState& st) {
