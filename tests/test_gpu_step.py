@@ -78,6 +78,21 @@ def test_fp8_step_matches_oracle(L, d, B, nc, sched, rounding):
     assert changed > 0                                                # the step did update weights
 
 
+@pytest.mark.parametrize("B", [1100, 2048])
+def test_fp8_step_large_batch(B):
+    """Several batch tiles in every kernel (forward N-tiles, grad_X M-tiles incl. a half-filled last
+    one, update K-steps), as the label-sharded runs see with an all-gathered batch."""
+    from oracle import xmc_oracle as O
+    L, d = 1536, 128
+    w, x, lab = _inputs(L, d, B, 4 * B, seed=B)
+    want_w, want_gx, want_loss = O.fp8_chunked_step([w], x, lab, 0.1, rounding="sr", seed=5, step=2,
+                                                    compute_loss=True)
+    got_w, g32, g16, loss = _run_gpu("fp8", [w], x, lab, 0.1, stochastic=True, step=2, loss=True, sched=512)
+    _check_weights(got_w, want_w)
+    assert rel_inf(g32, want_gx) < 1e-2
+    assert abs(loss - want_loss) < 1e-3 * abs(want_loss)
+
+
 def test_fp8_step_with_subnormal_weights():
     """Most stored weights below 2^-6 (e4m3 subnormals): exercises the in-kernel e4m3 -> bf16
     operand conversion of grad_X and stochastic rounding on the uniform part of the grid."""
