@@ -14,7 +14,7 @@ _DEFS = os.environ.get("XMC_NVCC_DEFS", "").split()
 _TAG = ("_" + "_".join(d.lstrip("-D").replace("=", "") for d in _DEFS)) if _DEFS else ""
 LIB = os.path.join(OUT_DIR, f"libelmo_xmc{_TAG}.so")
 SOURCES = ["xmc_lib.cu"]
-HEADERS = ["ptx.cuh", "numerics.cuh", "gemm_engine.cuh", "xmc_policies.cuh", "aux_kernels.cuh", "gradx_kernel.cuh",
+HEADERS = ["ptx.cuh", "numerics.cuh", "gemm_engine.cuh", "gemm_engine2.cuh", "xmc_policies.cuh", "aux_kernels.cuh", "gradx_kernel.cuh",
            os.path.join("..", "..", "include", "elmo_xmc.h")]
 
 

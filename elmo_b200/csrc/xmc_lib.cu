@@ -13,6 +13,7 @@
 #include "../../include/elmo_xmc.h"
 #include "aux_kernels.cuh"
 #include "gemm_engine.cuh"
+#include "gemm_engine2.cuh"
 #include "gradx_kernel.cuh"
 #include "xmc_policies.cuh"
 
@@ -122,6 +123,19 @@ int launch_gemm(const CUtensorMap& a, const CUtensorMap& b, const typename Polic
   CU_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, xmc::kSmemBytes));
   const int grid = grid_override > 0 ? grid_override : std::min(n_tiles, sm_count);
   kern<<<grid, 64 + 32 * Policy::kEpiWarps, xmc::kSmemBytes, stream>>>(a, b, p);
+  CU_TRY(cudaGetLastError());
+  return XMC_OK;
+}
+
+// same, on CTA pairs (cluster of 2): n_tiles counts 256-row pair tiles
+template <class Policy>
+int launch_gemm2(const CUtensorMap& a, const CUtensorMap& b, const typename Policy::Params& p, int n_tiles,
+                 int sm_count, cudaStream_t stream, int pairs_override = 0) {
+  if (n_tiles <= 0) return XMC_OK;
+  auto kern = xmc::gemm2_kernel<Policy>;
+  CU_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, xmc::kSmem2Bytes));
+  const int pairs = pairs_override > 0 ? pairs_override : std::min(n_tiles, sm_count / 2);
+  kern<<<2 * pairs, 64 + 32 * Policy::kEpiWarps, xmc::kSmem2Bytes, stream>>>(a, b, p);
   CU_TRY(cudaGetLastError());
   return XMC_OK;
 }
@@ -892,20 +906,29 @@ int xmc_test_gemm(int32_t device, int32_t layout, int32_t dtype, int32_t M, int3
   CUtensorMap ma, mb;
   xmc::PlainParams p;
   p.M = M; p.N = N;
-  p.n_mtiles = cdiv(M, 128);
   p.n_ntiles = cdiv(N, 256);
   p.D = D;
   p.checksum_only = (layout & 2) ? 1 : 0;
+  const bool pair_mode = (layout & 4) != 0;
   layout &= 1;
+  if (pair_mode && layout == 1) { cudaFree(status); return fail(XMC_ERR_INVALID, "CTA pairs take K-major operands"); }
+  p.m_rows = pair_mode ? 256 : 128;
+  p.n_mtiles = cdiv(M, p.m_rows);
   p.status = status;
   int rc = XMC_OK;
   if (layout == 0) {
     if ((rc = make_map_kmajor(&ma, f8, A, K, M, K, 128))) { cudaFree(status); return rc; }
-    if ((rc = make_map_kmajor(&mb, f8, B, K, N, K, 256))) { cudaFree(status); return rc; }
+    // a CTA of a pair stages only its half of the B rows
+    if ((rc = make_map_kmajor(&mb, f8, B, K, N, K, pair_mode ? 128 : 256))) { cudaFree(status); return rc; }
     p.k_steps = cdiv((long long)K * (f8 ? 1 : 2), 128);
-    for (int r = 0; r < repeat && rc == XMC_OK; ++r)
-      rc = f8 ? launch_gemm<xmc::PlainPolicy<true, false>>(ma, mb, p, p.n_mtiles * p.n_ntiles, sm_count, st)
-              : launch_gemm<xmc::PlainPolicy<false, false>>(ma, mb, p, p.n_mtiles * p.n_ntiles, sm_count, st);
+    for (int r = 0; r < repeat && rc == XMC_OK; ++r) {
+      if (pair_mode)
+        rc = f8 ? launch_gemm2<xmc::PlainPolicy<true, false>>(ma, mb, p, p.n_mtiles * p.n_ntiles, sm_count, st)
+                : launch_gemm2<xmc::PlainPolicy<false, false>>(ma, mb, p, p.n_mtiles * p.n_ntiles, sm_count, st);
+      else
+        rc = f8 ? launch_gemm<xmc::PlainPolicy<true, false>>(ma, mb, p, p.n_mtiles * p.n_ntiles, sm_count, st)
+                : launch_gemm<xmc::PlainPolicy<false, false>>(ma, mb, p, p.n_mtiles * p.n_ntiles, sm_count, st);
+    }
   } else {
     if ((rc = make_map_mnmajor(&ma, A, M, K, M))) { cudaFree(status); return rc; }
     if ((rc = make_map_mnmajor(&mb, B, N, K, N))) { cudaFree(status); return rc; }

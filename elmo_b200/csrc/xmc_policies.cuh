@@ -608,6 +608,7 @@ struct TopkPolicy {
 // Plain D = A B^T, fp32 out (engine self-test; also the logits kernel's skeleton)
 // -------------------------------------------------------------------------------------------------
 struct PlainParams {
+  int m_rows;              // rows per M tile: 128 (one CTA) or 256 (CTA pair)
   int M, N;
   int n_mtiles, n_ntiles;
   int k_steps;
@@ -629,7 +630,7 @@ struct PlainPolicy {
   __device__ static void job(const Params& p, int tile, Job& j) {
     j.t0 = tile / p.n_ntiles;
     j.t1 = tile - j.t0 * p.n_ntiles;
-    j.a0 = j.t0 * kTileM;
+    j.a0 = j.t0 * p.m_rows;
     j.b0 = j.t1 * kTileN;
     j.k_begin = 0;
     j.k_steps = p.k_steps;

@@ -181,6 +181,7 @@ int xmc_large_k_matmul_noalloc(int32_t device, const void* a_bf16, const void* b
  *   layout 0: A [M x K], B [N x K] both K-major (row-major as written), dtype XMC_DT_BF16 or XMC_DT_E4M3
  *   layout 1: A given as [K x M], B as [K x N] row-major (both "MN-major"), dtype XMC_DT_BF16
  *   layout | 2: same contraction, but D is not stored (times the main loop alone)
+ *   layout | 4: layout 0 on CTA pairs (cluster of two, tcgen05 cta_group::2)
  * M, N, K arbitrary positive (rows 16-byte aligned: inner extents multiples of 8 (bf16) / 16 (e4m3)).
  */
 int xmc_test_gemm(int32_t device, int32_t layout, int32_t dtype, int32_t M, int32_t N, int32_t K,
