@@ -51,7 +51,6 @@ struct SharedTail {
   uint32_t tmem_base;
   Ctl ctl;
   uint32_t bitmap[kTileM * (kTileN / 32)];   // positives of one (label tile, batch tile)
-  alignas(16) uint8_t stage[8 * 2048];       // per-warp store staging (epilogues with up to 8 warps)
 };
 
 constexpr int kSmemBytes = kStages * kStageBytes + (int)sizeof(SharedTail) + 1024;

@@ -29,10 +29,9 @@ struct SharedTail2 {
   uint32_t tmem_base;
   Ctl ctl;
   uint32_t bitmap[kTileM * (kTileN / 32)];
-  alignas(16) uint8_t stage[8 * 2048];
 };
-// the epilogues address `bitmap` and `stage` through SharedTail: keep the layouts of those two
-// members interchangeable by handing the policies a SharedTail view of the tail's end
+// the epilogues address `bitmap` through SharedTail: hand the policies a SharedTail view whose
+// bitmap member coincides with this one
 static_assert(sizeof(SharedTail2) - offsetof(SharedTail2, bitmap) == sizeof(SharedTail) - offsetof(SharedTail, bitmap),
               "tail layouts diverged");
 
@@ -47,7 +46,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   SharedTail2& sh = *reinterpret_cast<SharedTail2*>(smem + kStages2 * kStage2Bytes);
-  // view for the policies: same bitmap/stage members
+  // view for the policies: same bitmap member
   SharedTail& shp = *reinterpret_cast<SharedTail*>(reinterpret_cast<uint8_t*>(&sh) + offsetof(SharedTail2, bitmap) -
                                                    offsetof(SharedTail, bitmap));
   const int warp = threadIdx.x >> 5;

@@ -333,7 +333,7 @@ int xmc_bind_weights(xmc_handle* h, int32_t n_chunks, void* const* ptrs, const i
   DeviceGuard guard(h->cfg.device);
   int64_t total = 0;
   for (int i = 0; i < n_chunks; ++i) {
-    if (ptrs[i] == nullptr || ((uintptr_t)ptrs[i] & 15u)) return fail(XMC_ERR_INVALID, "weight chunk %d: null or not 16-byte aligned", i);
+    if (ptrs[i] == nullptr || ((uintptr_t)ptrs[i] & 31u)) return fail(XMC_ERR_INVALID, "weight chunk %d: null or not 32-byte aligned", i);
     if (rows[i] <= 0) return fail(XMC_ERR_INVALID, "weight chunk %d has %lld rows", i, (long long)rows[i]);
     if (i + 1 < n_chunks && rows[i] != rows[0]) return fail(XMC_ERR_INVALID, "all weight chunks but the last must have equal rows (chunk %d: %lld vs %lld)", i, (long long)rows[i], (long long)rows[0]);
     if (i + 1 == n_chunks && rows[i] > rows[0]) return fail(XMC_ERR_INVALID, "last weight chunk is larger than the others");
@@ -511,6 +511,7 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
         if (int rc = make_map_kmajor(&map_w, false, w16, d, rows_valid, d, 128)) return rc;
       }
       xmc::FwdParams fp;
+      fp.m_rows = 128;
       fp.rows_valid = rows_valid;
       fp.n_ltiles = n_lt;
       fp.n_btiles = cdiv(bpad, 256);

@@ -20,6 +20,7 @@ struct NoState {};
 // the positives with set semantics (:108).
 // -------------------------------------------------------------------------------------------------
 struct FwdParams {
+  int m_rows;              // label rows per M tile: 128 (one CTA) or 256 (CTA pair)
   int rows_valid;          // label rows of this scheduling chunk
   int n_ltiles, n_btiles;  // label tiles (128) x batch tiles (256)
   int batch, bpad;         // valid batch rows, padded row length of G (multiple of 16)
@@ -44,7 +45,6 @@ struct FwdPolicy {
 #define XMC_FWD_WARPS 8
 #endif
   static constexpr int kEpiWarps = XMC_FWD_WARPS;
-  static_assert(kEpiWarps <= 8, "the store staging buffer holds 8 warps");
   struct EpilogueState {
     float loss;
     int has_pos;
@@ -54,7 +54,7 @@ struct FwdPolicy {
   __device__ static void job(const Params& p, int tile, Job& j) {
     j.t0 = tile / p.n_btiles;          // label tile
     j.t1 = tile - j.t0 * p.n_btiles;   // batch tile
-    j.a0 = j.t0 * kTileM;
+    j.a0 = j.t0 * p.m_rows;
     j.b0 = j.t1 * kTileN;
     j.k_begin = 0;
     j.k_steps = p.k_steps;
@@ -68,7 +68,8 @@ struct FwdPolicy {
   // Each warp owns the bitmap words of its rows (quarter q) and of its column groups (phase h).
   __device__ static void epilogue_pre(const Params& p, const Job& j, SharedTail& sh, const EpiCtx& ec,
                                       EpilogueState& st) {
-    const int beg = p.bucket_off[p.tile_base + j.t0], end = p.bucket_off[p.tile_base + j.t0 + 1];
+    const int bkt = p.tile_base + (j.a0 >> 7);      // buckets are per 128 label rows
+    const int beg = p.bucket_off[bkt], end = p.bucket_off[bkt + 1];
     st.has_pos = end > beg;
     if (!st.has_pos) return;
     constexpr int kWordsPerRow = kTileN / 32;
@@ -146,26 +147,17 @@ struct FwdPolicy {
           else if (b + 1 >= p.batch) out[i] &= 0x0000FFFFu;
         }
       }
-      // Store through a per-warp 2 KB staging buffer so that every store instruction writes whole
-      // 64-byte runs of a row (4 lanes per row) instead of 32 scattered 16-byte pieces: lane = row
-      // writes its 64 B into shared memory (16-byte slots XOR-swizzled by row so that neither phase
-      // has bank conflicts), then lane L re-reads slot (L & 3) of row 8*i + (L >> 2).
-      uint8_t* stg = sh.stage + ec.slot * 2048;
-      const int lr = ec.lane;
+      // two 256-bit stores: every thread writes whole 32-byte sectors of its row
+      __nv_bfloat16* grow = p.G + (size_t)crow * p.bpad + j.b0 + c0;
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
-        *reinterpret_cast<uint4*>(stg + lr * 64 + ((c ^ ((lr >> 1) & 3)) << 4)) =
-            make_uint4(out[4 * c], out[4 * c + 1], out[4 * c + 2], out[4 * c + 3]);
-      __syncwarp();
-      const int tile_row0 = j.a0 + ec.q * 32;
+      for (int i = 0; i < 2; ++i) {
+        if (j.b0 + c0 + 16 * i < p.bpad) {
+          U32x8 o8;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int r = 8 * i + (lr >> 2), c = lr & 3;
-        const uint4 val = *reinterpret_cast<const uint4*>(stg + r * 64 + ((c ^ ((r >> 1) & 3)) << 4));
-        if (j.b0 + c0 + 8 * c < p.bpad)
-          *reinterpret_cast<uint4*>(p.G + (size_t)(tile_row0 + r) * p.bpad + j.b0 + c0 + 8 * c) = val;
+          for (int k = 0; k < 8; ++k) o8.v[k] = out[8 * i + k];
+          st_global_256(grow + 16 * i, o8);
+        }
       }
-      __syncwarp();
     }
   }
   __device__ static void epilogue_end(const Params& p, SharedTail&, const EpiCtx& ec, EpilogueState& st) {
@@ -283,6 +275,7 @@ struct UpdPolicy {
                                     unsigned long long elem, uint8_t* dst, bool store_lo, bool store_hi) {
     uint32_t r[16];
     if (SR) random32(p, elem, r);
+    U32x8 res;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const uint32_t rw[4] = {w16[h].x, w16[h].y, w16[h].z, w16[h].w};
@@ -303,9 +296,9 @@ struct UpdPolicy {
         }
         ow[k] = (uint32_t)float2_to_e4m3x2(o[0], o[1]) | ((uint32_t)float2_to_e4m3x2(o[2], o[3]) << 16);
       }
-      if (h == 0 ? store_lo : store_hi)
-        *reinterpret_cast<uint4*>(dst + 16 * h) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+      res.v[4 * h] = ow[0]; res.v[4 * h + 1] = ow[1]; res.v[4 * h + 2] = ow[2]; res.v[4 * h + 3] = ow[3];
     }
+    if (store_lo) st_global_256(dst, res);       // one whole sector per thread
   }
 
   // Kahan-compensated rows: w = W + D - lr*acc; W' = round(w); D' = cast(D + W - W' - lr*acc)
@@ -419,10 +412,14 @@ struct UpdPolicy {
       if constexpr (W8) {
         uint8_t* wp = reinterpret_cast<uint8_t*>(p.W) + (size_t)crow * p.d + col;
         uint4 w16[2];
-#pragma unroll
-        for (int h = 0; h < 2; ++h)
-          w16[h] = (row_valid && col + 16 * h < p.d) ? *reinterpret_cast<const uint4*>(wp + 16 * h)
-                                                     : make_uint4(0, 0, 0, 0);
+        {
+          // d is a multiple of 64 and col of 32: the 32-byte segment is inside the row or absent
+          U32x8 raw;
+          if (row_valid && col < p.d) raw = ld_global_256(wp);
+          else raw = U32x8{{0, 0, 0, 0, 0, 0, 0, 0}};
+          w16[0] = make_uint4(raw.v[0], raw.v[1], raw.v[2], raw.v[3]);
+          w16[1] = make_uint4(raw.v[4], raw.v[5], raw.v[6], raw.v[7]);
+        }
         load_acc(taddr + c0, have_acc, v);
         if constexpr (KAHAN) {
           if (row_valid && crow < p.kahan_rows) {

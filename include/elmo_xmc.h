@@ -79,7 +79,7 @@ int xmc_destroy(xmc_handle* h);
 
 /*
  * Bind the weight storage: n_chunks row-major [rows[i] x dim] device arrays (bf16 in
- * XMC_MODE_BF16, else e4m3), 16-byte aligned, borrowed -- never freed by the library.
+ * XMC_MODE_BF16, else e4m3), 32-byte aligned, borrowed -- never freed by the library.
  * All chunks but the last must have the same number of rows.  The label rows of the handle are
  * the concatenation of the chunks; row r of the concatenation has global id label_offset + r.
  */
