@@ -378,20 +378,19 @@ struct UpdPolicy {
     uint32_t r[16];
     if (SR) random32(p, elem, r);
 #pragma unroll
-    for (int g8 = 0; g8 < 4; ++g8) {
-      if (g8 >= 2 * valid16) break;
-      const uint4 raw = *reinterpret_cast<const uint4*>(wp + 8 * g8);
-      const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
-      uint32_t ow[4];
+    for (int g16 = 0; g16 < 2; ++g16) {          // 16 bf16 = one 32-byte sector per access
+      if (g16 >= valid16) break;
+      const U32x8 raw = ld_global_256(wp + 16 * g16);
+      U32x8 ow;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int e = 8 * g8 + 2 * i;
-        const float o0 = new_weight(p, bf16_bits_to_float(rw[i] & 0xFFFFu), v[e]);
-        const float o1 = new_weight(p, bf16_bits_to_float(rw[i] >> 16), v[e + 1]);
-        if (SR) ow[i] = sr_bf16_bits(o0, r16_of(r, e)) | (sr_bf16_bits(o1, r16_of(r, e + 1)) << 16);
-        else ow[i] = pack_bf16x2(o0, o1);
+      for (int i = 0; i < 8; ++i) {
+        const int e = 16 * g16 + 2 * i;
+        const float o0 = new_weight(p, bf16_bits_to_float(raw.v[i] & 0xFFFFu), v[e]);
+        const float o1 = new_weight(p, bf16_bits_to_float(raw.v[i] >> 16), v[e + 1]);
+        if (SR) ow.v[i] = sr_bf16_bits(o0, r16_of(r, e)) | (sr_bf16_bits(o1, r16_of(r, e + 1)) << 16);
+        else ow.v[i] = pack_bf16x2(o0, o1);
       }
-      *reinterpret_cast<uint4*>(wp + 8 * g8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+      st_global_256(wp + 16 * g16, ow);
     }
   }
 
@@ -497,7 +496,15 @@ struct LogitsPolicy {
 #pragma unroll
       for (int i = 0; i < 16; ++i)
         o[i] = pack_bf16x2(__uint_as_float(v[2 * i]) * p.w_scale, __uint_as_float(v[2 * i + 1]) * p.w_scale);
-      if (valid == 32 && (((uintptr_t)dst) & 15u) == 0) {
+      if (valid == 32 && (((uintptr_t)dst) & 31u) == 0) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          U32x8 o8;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) o8.v[k] = o[8 * i + k];
+          st_global_256(dst + 16 * i, o8);
+        }
+      } else if (valid == 32 && (((uintptr_t)dst) & 15u) == 0) {
 #pragma unroll
         for (int i = 0; i < 4; ++i)
           reinterpret_cast<uint4*>(dst)[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
