@@ -106,8 +106,10 @@ gradx_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant__ 
     tmem_alloc(smem_u32(&sh.tmem_base), kTmemCols);
     tmem_relinquish();
   }
+  pdl_launch_dependents();                  // the next kernel may start its prologue as SMs free up
   tc_fence_before();
   __syncthreads();
+  pdl_wait();                               // nothing above touches global memory written by earlier kernels
   tc_fence_after();
   const uint32_t tmem_base = sh.tmem_base;
 

@@ -6,6 +6,11 @@
 #include <stdint.h>
 
 namespace xmc {
+// Programmatic dependent launch: let the next kernel of the stream be scheduled while this one drains,
+// and hold this kernel's first global access until everything before it in the stream has completed.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 
 // ---------------------------------------------------------------------------------------------
 // Device status word: kernels never trap or spin forever; a wait that exceeds its time limit

@@ -114,6 +114,25 @@ int make_map_mnmajor(CUtensorMap* m, const void* base, uint64_t mn, uint64_t k_r
   return make_map(m, false, base, mn, k_rows, row_stride_elems * 2, 64, box_rows);
 }
 
+// Launch with programmatic stream serialization: the kernel may be scheduled while its predecessor in
+// the stream drains; it orders itself with griddepcontrol.wait before its first global access.
+template <class Kern, class... Args>
+cudaError_t launch_pdl(Kern kern, int grid, int block, size_t smem, cudaStream_t stream, const Args&... args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3((unsigned)block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  static const bool off = getenv("XMC_NO_PDL") != nullptr;
+  cfg.attrs = at;
+  cfg.numAttrs = off ? 0 : 1;
+  return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
 template <class Policy>
 int launch_gemm(const CUtensorMap& a, const CUtensorMap& b, const typename Policy::Params& p, int n_tiles,
                 int sm_count, cudaStream_t stream, int grid_override = 0) {
@@ -122,8 +141,7 @@ int launch_gemm(const CUtensorMap& a, const CUtensorMap& b, const typename Polic
   // per device and cheap; one process may drive several devices
   CU_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, xmc::kSmemBytes));
   const int grid = grid_override > 0 ? grid_override : std::min(n_tiles, sm_count);
-  kern<<<grid, 64 + 32 * Policy::kEpiWarps, xmc::kSmemBytes, stream>>>(a, b, p);
-  CU_TRY(cudaGetLastError());
+  CU_TRY(launch_pdl(kern, grid, 64 + 32 * Policy::kEpiWarps, xmc::kSmemBytes, stream, a, b, p));
   return XMC_OK;
 }
 
@@ -561,10 +579,10 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
         const int grid = n_bt * n_dt * n_splits;
         if (w8) {
           CU_TRY(cudaFuncSetAttribute(xmc::gradx_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, xmc::kGxSmemBytes));
-          xmc::gradx_kernel<true><<<grid, xmc::kGxThreads, xmc::kGxSmemBytes, st>>>(map_g_mn, map_w_gx, gp);
+          CU_TRY(launch_pdl(xmc::gradx_kernel<true>, grid, xmc::kGxThreads, xmc::kGxSmemBytes, st, map_g_mn, map_w_gx, gp));
         } else {
           CU_TRY(cudaFuncSetAttribute(xmc::gradx_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, xmc::kGxSmemBytes));
-          xmc::gradx_kernel<false><<<grid, xmc::kGxThreads, xmc::kGxSmemBytes, st>>>(map_g_mn, map_w_gx, gp);
+          CU_TRY(launch_pdl(xmc::gradx_kernel<false>, grid, xmc::kGxThreads, xmc::kGxSmemBytes, st, map_g_mn, map_w_gx, gp));
         }
         CU_TRY(cudaGetLastError());
       }
@@ -949,3 +967,5 @@ int xmc_test_gemm(int32_t device, int32_t layout, int32_t dtype, int32_t M, int3
 }
 
 }  // extern "C"
+
+
