@@ -208,12 +208,16 @@ gradx_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant__ 
       tc_fence_after();
       const int q = warp & 3;
       const int hm = cw >> 2;                                     // warps 2..5 -> accumulator 0, 6..9 -> 1
-      const int b = b0 + hm * 128 + q * 32 + lane;
-      const bool row_valid = b < p.bpad && hm < m_halves;
       const bool have_acc = k_steps > 0;
       if (have_acc || !p.accumulate) {
-        float* dstp = p.partial + ((size_t)split * p.bpad + b) * p.d + c0;
+        // Drain through a per-warp 32 x 32 staging tile in the (now idle) operand stages so that the
+        // global accesses run along rows: 8 lanes cover 128 contiguous bytes of one batch row instead
+        // of 32 lanes touching 32 different rows with 16 bytes each.
+        const int brow0 = b0 + hm * 128 + q * 32;                 // first batch row of this warp
+        float* dst0 = p.partial + ((size_t)split * p.bpad + brow0) * p.d + c0;
+        float4* stage = reinterpret_cast<float4*>(smem_a + cw * 4096);   // [32 rows][8 chunks of 16 B], XOR-swizzled
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + hm * 256;
+        const int rr = lane >> 3, ch = lane & 7;                  // read side: row within a group of 4, 16-byte chunk
         for (int cg = 0; cg < n_eff; cg += 32) {
           uint32_t v[32];
           if (have_acc && hm < m_halves) {
@@ -223,13 +227,19 @@ gradx_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant__ 
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = 0u;
           }
-          if (!row_valid) continue;
+          __syncwarp();                                           // the previous group's reads are done
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            if (c0 + cg + 4 * i >= p.d) continue;
-            float4 o = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
-                                   __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
-            float4* ptr = reinterpret_cast<float4*>(dstp + cg + 4 * i);
+          for (int i = 0; i < 8; ++i)
+            stage[lane * 8 + (i ^ (lane & 7))] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                                             __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+          __syncwarp();
+          const bool col_ok = c0 + cg + 4 * ch < p.d;             // d is a multiple of 4
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int r = 4 * j + rr;
+            const float4 o = stage[r * 8 + (ch ^ (r & 7))];
+            if (!col_ok || brow0 + r >= p.bpad || hm >= m_halves) continue;
+            float4* ptr = reinterpret_cast<float4*>(dst0 + (size_t)r * p.d + cg + 4 * ch);
             if (p.accumulate) {
               // Fire-and-forget vector reduction at L2: no read latency in the kernel's tail.  Each
               // element has exactly one writer per launch and launches are stream-ordered, so the
