@@ -129,6 +129,65 @@ __global__ void bucket_fill_kernel(const int32_t* __restrict__ labels, long long
   }
 }
 
+// Count, scan and fill in ONE launch of one 1024-thread block, for steps whose positives are few
+// (the usual case: a few thousand pairs): three launches and a memset less per step.
+// count[0..n) and cursor[0..n) need no prior clearing.
+__global__ void __launch_bounds__(1024, 1)
+bucket_all_kernel(const int32_t* __restrict__ labels, int nnz, int batch, BucketGeom g, int n,
+                  int* count, int* cursor, int* off, uint32_t* __restrict__ entries, int* status) {
+  __shared__ int warp_sum[32];
+  __shared__ int carry;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    count[i] = 0;
+    cursor[i] = 0;
+  }
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < nnz; i += blockDim.x) {
+    int bucket, lrow;
+    if (bucket_of(g, labels[2 * i], labels[2 * i + 1], batch, status, bucket, lrow)) atomicAdd(&count[bucket], 1);
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int base = 0; base < n; base += blockDim.x) {
+    const int i = base + threadIdx.x;
+    const int v = i < n ? __ldcg(&count[i]) : 0;          // written by atomics: read at L2
+    int s = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, s, o);
+      if (lane >= o) s += t;
+    }
+    if (lane == 31) warp_sum[warp] = s;
+    __syncthreads();
+    if (warp == 0) {
+      int w = warp_sum[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, w, o);
+        if (lane >= o) w += t;
+      }
+      warp_sum[lane] = w;
+    }
+    __syncthreads();
+    const int before = carry + (warp > 0 ? warp_sum[warp - 1] : 0) + s - v;
+    if (i < n) off[i] = before;
+    __syncthreads();
+    if (threadIdx.x == blockDim.x - 1) carry = before + v;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) off[n] = carry;
+  __syncthreads();                                          // off[] written by this block is visible to it
+  for (int i = threadIdx.x; i < nnz; i += blockDim.x) {
+    int bucket, lrow;
+    const int row = labels[2 * i];
+    if (bucket_of(g, row, labels[2 * i + 1], batch, nullptr, bucket, lrow)) {
+      const int pos = atomicAdd(&cursor[bucket], 1);
+      entries[off[bucket] + pos] = (uint32_t)row | ((uint32_t)lrow << 16);
+    }
+  }
+}
+
 // e4m3 -> bf16 staging of one scheduling chunk of weights (exact); n16 = number of 16-byte groups
 __global__ void e4m3_to_bf16_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long long n16) {
   const long long stride = (long long)gridDim.x * blockDim.x;

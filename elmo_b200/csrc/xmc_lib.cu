@@ -445,16 +445,20 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
     if (int rc = dev_alloc(h, (void**)&h->entries, (size_t)h->ent_cap * 4, false)) return rc;
   }
   const xmc::BucketGeom geom = geom_of(h);
-  CU_TRY(cudaMemsetAsync(h->bucket_cnt, 0, (size_t)h->n_buckets * 8, st));
-  if (nnz > 0) {
+  if (nnz <= 131072) {
+    // few positives: one single-block launch does the clearing, the count, the scan and the fill
+    mark(h, K_PREP, st);
+    xmc::bucket_all_kernel<<<1, 1024, 0, st>>>(labels, (int)nnz, batch, geom, h->n_buckets, h->bucket_cnt,
+                                               h->bucket_cnt + h->n_buckets, h->bucket_off, h->entries, h->status);
+    CU_TRY(cudaGetLastError());
+  } else {
+    CU_TRY(cudaMemsetAsync(h->bucket_cnt, 0, (size_t)h->n_buckets * 8, st));
     mark(h, K_PREP, st);
     xmc::bucket_count_kernel<<<cdiv(nnz, 256), 256, 0, st>>>(labels, nnz, batch, geom, h->bucket_cnt, h->status);
     CU_TRY(cudaGetLastError());
-  }
-  mark(h, K_PREP, st);
-  xmc::bucket_scan_kernel<<<1, 1024, 0, st>>>(h->bucket_cnt, h->n_buckets, h->bucket_off);
-  CU_TRY(cudaGetLastError());
-  if (nnz > 0) {
+    mark(h, K_PREP, st);
+    xmc::bucket_scan_kernel<<<1, 1024, 0, st>>>(h->bucket_cnt, h->n_buckets, h->bucket_off);
+    CU_TRY(cudaGetLastError());
     mark(h, K_PREP, st);
     xmc::bucket_fill_kernel<<<cdiv(nnz, 256), 256, 0, st>>>(labels, nnz, batch, geom, h->bucket_off,
                                                             h->bucket_cnt + h->n_buckets, h->entries);

@@ -189,3 +189,17 @@ def test_two_steps_are_deterministic_and_use_fresh_bits():
     assert torch.equal(a[0][0].view(torch.uint8), b[0][0].view(torch.uint8))
     assert torch.equal(a[1], b[1])                                    # grad_X bit-reproducible
     assert not torch.equal(a[0][0].view(torch.uint8), c[0][0].view(torch.uint8))
+
+
+def test_many_positives_take_the_multi_launch_bucketing_path():
+    """More than 131072 label pairs: the positives are bucketed by the count / scan / fill launches
+    instead of the single-block kernel; the step must still match the oracle."""
+    from oracle import xmc_oracle as O
+    L, d, B = 2048, 64, 512
+    w, x, lab = _inputs(L, d, B, 140_000, seed=77)
+    assert lab.shape[0] > 131072
+    want_w, want_gx, want_loss = O.fp8_chunked_step([w], x, lab, 0.5, rounding="rn", compute_loss=True)
+    got_w, g32, _, loss = _run_gpu("fp8", [w], x, lab, 0.5, stochastic=False, loss=True, sched=512)
+    _check_weights(got_w, want_w)
+    assert rel_inf(g32, want_gx) < 1e-2
+    assert abs(loss - want_loss) <= 1e-3 * abs(want_loss)
