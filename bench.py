@@ -304,7 +304,7 @@ def run_ours(args, wl, rank, local_rank, world):
     # DRAM bytes per label row of one launch (dram__bytes_read.sum + dram__bytes_write.sum of an ncu
     # capture of a 65 536-row chunk at batch 512, d 768: profiles/step_kernels_small_case.md); traffic
     # grows with the rows a launch processes, so it is scaled to this run's rows per launch
-    dram_per_row = {"update": 134.1e6 / 65536, "grad_x": 159.3e6 / 65536, "forward": 71.2e6 / 65536}
+    dram_per_row = {"update": 133.8e6 / 65536, "grad_x": 159.1e6 / 65536, "forward": 69.3e6 / 65536}
     rows_per_launch = (L / world) / max(dom_launches, 1.0)
     traffic = dram_per_row[dominant] * rows_per_launch if (wl.dim == 768 and b_loc * world == 512) else None
     fp8_dom = dominant == "forward" and wl.mode == "fp8"

@@ -148,34 +148,38 @@ bucket_all_kernel(const int32_t* __restrict__ labels, int nnz, int batch, Bucket
     if (bucket_of(g, labels[2 * i], labels[2 * i + 1], batch, status, bucket, lrow)) atomicAdd(&count[bucket], 1);
   }
   __syncthreads();
+  // exclusive scan: every thread sums a contiguous run of buckets, one block-wide scan of the 1024
+  // run totals, then each thread writes the offsets of its run
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int base = 0; base < n; base += blockDim.x) {
-    const int i = base + threadIdx.x;
-    const int v = i < n ? __ldcg(&count[i]) : 0;          // written by atomics: read at L2
-    int s = v;
+  const int per = (n + (int)blockDim.x - 1) / (int)blockDim.x;
+  const int beg = min(n, (int)threadIdx.x * per), end = min(n, beg + per);
+  int run = 0;
+  for (int i = beg; i < end; ++i) run += __ldcg(&count[i]);  // written by atomics: read at L2
+  int s = run;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, s, o);
+    if (lane >= o) s += t;
+  }
+  if (lane == 31) warp_sum[warp] = s;
+  __syncthreads();
+  if (warp == 0) {
+    int w = warp_sum[lane];
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-      const int t = __shfl_up_sync(0xffffffffu, s, o);
-      if (lane >= o) s += t;
+      const int t = __shfl_up_sync(0xffffffffu, w, o);
+      if (lane >= o) w += t;
     }
-    if (lane == 31) warp_sum[warp] = s;
-    __syncthreads();
-    if (warp == 0) {
-      int w = warp_sum[lane];
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int t = __shfl_up_sync(0xffffffffu, w, o);
-        if (lane >= o) w += t;
-      }
-      warp_sum[lane] = w;
-    }
-    __syncthreads();
-    const int before = carry + (warp > 0 ? warp_sum[warp - 1] : 0) + s - v;
-    if (i < n) off[i] = before;
-    __syncthreads();
-    if (threadIdx.x == blockDim.x - 1) carry = before + v;
-    __syncthreads();
+    warp_sum[lane] = w;
   }
+  __syncthreads();
+  int before = (warp > 0 ? warp_sum[warp - 1] : 0) + s - run;
+  for (int i = beg; i < end; ++i) {
+    off[i] = before;
+    before += __ldcg(&count[i]);
+  }
+  if (threadIdx.x == blockDim.x - 1) carry = before;        // the last thread's run ends at n (or is empty)
+  __syncthreads();
   if (threadIdx.x == 0) off[n] = carry;
   __syncthreads();                                          // off[] written by this block is visible to it
   for (int i = threadIdx.x; i < nnz; i += blockDim.x) {
