@@ -168,6 +168,7 @@ struct xmc_handle {
   int sm_count = 0;
   int bpad_max = 0;
   int sched = 0;
+  int64_t g_rows = 0;              // rows of G / w16 currently allocated
   std::vector<void*> w_ptrs;
   std::vector<int64_t> w_rows;
   int64_t total_rows = 0;
@@ -311,8 +312,8 @@ int xmc_create(const xmc_config* cfg, xmc_handle** out) {
   A((void**)&h->x8, xrows * d, true);
   A((void**)&h->x16, xrows * d * 2, true);
   A((void**)&h->xt, (size_t)std::max(d, 256) * h->bpad_max * 2, true);
-  A((void**)&h->G, (size_t)h->sched * h->bpad_max * 2, true);
-  if (cfg->mode == XMC_MODE_SIMFP8) A((void**)&h->w16, (size_t)h->sched * d * 2, true);
+  // G (and the bf16 staging copy of the simulated-FP8 forward) are sized when the weights are bound:
+  // they never need more rows than the largest weight chunk.
   h->partial_floats = std::max<int64_t>((int64_t)h->sm_count * 256 * 256, (int64_t)h->bpad_max * round_up(d, 256));
   A((void**)&h->partial, (size_t)h->partial_floats * 4, true);
   A((void**)&h->status, 4 * sizeof(int), true);
@@ -362,6 +363,18 @@ int xmc_bind_weights(xmc_handle* h, int32_t n_chunks, void* const* ptrs, const i
   h->w_rows.assign(rows, rows + n_chunks);
   h->total_rows = total;
   h->rows_per_chunk = rows[0];
+  const int64_t g_rows = std::min<int64_t>(h->sched, round_up(h->rows_per_chunk, 128));
+  if (g_rows > h->g_rows) {
+    const int d = h->cfg.dim;
+    if (h->G) { cudaFree(h->G); h->ws_bytes -= h->g_rows * h->bpad_max * 2; h->G = nullptr; }
+    if (h->w16) { cudaFree(h->w16); h->ws_bytes -= h->g_rows * d * 2; h->w16 = nullptr; }
+    h->g_rows = 0;
+    if (int rc = dev_alloc(h, (void**)&h->G, (size_t)g_rows * h->bpad_max * 2, true)) return rc;
+    if (h->cfg.mode == XMC_MODE_SIMFP8) {
+      if (int rc = dev_alloc(h, (void**)&h->w16, (size_t)g_rows * d * 2, true)) return rc;
+    }
+    h->g_rows = g_rows;
+  }
   const int spc = cdiv(h->rows_per_chunk, h->sched);
   const int nb = n_chunks * spc * (h->sched / 128);
   if (nb != h->n_buckets) {
@@ -494,8 +507,8 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
     if (int rc = make_map_kmajor(&map_x, false, h->x16, d, xrows, d, 256)) return rc;
   }
   if (int rc = make_map_kmajor(&map_xt, false, h->xt, bpad, std::max(d, 256), bpad, 256)) return rc;
-  if (int rc = make_map_kmajor(&map_g_k, false, h->G, bpad, h->sched, bpad, 128)) return rc;
-  if (int rc = make_map_blocked(&map_g_mn, false, h->G, bpad, h->sched, bpad, xmc::kGxRows, true)) return rc;
+  if (int rc = make_map_kmajor(&map_g_k, false, h->G, bpad, h->g_rows, bpad, 128)) return rc;
+  if (int rc = make_map_blocked(&map_g_mn, false, h->G, bpad, h->g_rows, bpad, xmc::kGxRows, true)) return rc;
 
   const float lr_eff = lr / h->cfg.w_scale;
   const int tiles_per_sched = h->sched / 128;
