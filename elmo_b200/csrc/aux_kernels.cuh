@@ -225,49 +225,95 @@ __global__ void reduce_gradx_kernel(const float* __restrict__ partial, int n_spl
   }
 }
 
-// Final top-k of one batch row from the candidate lists left by the top-k launches.  One block per
-// row; k rounds of "block-wide best remaining candidate" (value descending, then id ascending).
-// Candidate (launch l, CTA c, slot s, lane) belongs to row (c % n_mtiles)*128 + (s & 3 mapped to its
-// TMEM quarter)*32 + lane; list_of_row enumerates exactly those lists.
-__global__ void topk_merge_kernel(float* __restrict__ cand_val, int* __restrict__ cand_idx, int n_launch,
-                                  int grid, int n_mtiles, int k, int batch, long long label_offset,
-                                  float* __restrict__ out_val, int* __restrict__ out_idx) {
+// State of the fused top-k before its first launch: empty lists, thresholds at -inf.
+__global__ void topk_init_kernel(int* __restrict__ list_cnt, float* __restrict__ list_thr, int lists,
+                                 unsigned int* __restrict__ row_thr, int rows) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < lists) {
+    list_cnt[i] = 0;
+    list_thr[i] = -INFINITY;
+  }
+  if (i < rows) row_thr[i] = 0x007FFFFFu;                // ordered key of -inf
+}
+
+// Final top-k of one batch row from the candidate lists of the top-k launches.  One block per row.
+// The row's lists are (CTA c with c % n_mtiles == row tile, the two epilogue warps of the row's TMEM
+// quarter, lane).  Candidates below the row's published threshold cannot be among the k best and are
+// dropped while the rest is gathered into shared memory; then k rounds of "block-wide best remaining
+// candidate" (value descending, id ascending).  If the gathered set does not fit, the rounds run over
+// the lists in global memory instead.
+constexpr int kTopkGather = 4096;
+__global__ void __launch_bounds__(256)
+topk_merge_kernel(const float* __restrict__ cand_val, int* __restrict__ cand_idx, const int* __restrict__ list_cnt,
+                  const unsigned int* __restrict__ row_thr, int cap, int grid, int n_mtiles, int k, int batch,
+                  long long label_offset, float* __restrict__ out_val, int* __restrict__ out_idx) {
   const int b = blockIdx.x;
   if (b >= batch) return;
   const int mt = b >> 7, q = (b >> 5) & 3, lane = b & 31;
-  const int ctas = grid / n_mtiles;                     // CTAs per batch tile in every launch
-  const int lists = n_launch * ctas * 2;                // two epilogue warps (column phases) per quarter
-  const long long total = (long long)lists * k;
-  __shared__ float s_val[32];
-  __shared__ long long s_pos[32];
-  __shared__ int s_id[32];
-  for (int round = 0; round < k; ++round) {
-    float best = -INFINITY;
-    long long best_pos = -1;
-    int best_id = 0x7fffffff;
-    for (long long t = threadIdx.x; t < total; t += blockDim.x) {
-      const int li = (int)(t / k), e = (int)(t - (long long)li * k);
-      const int l = li / (ctas * 2), r = li - l * ctas * 2;
-      const int c = (r >> 1) * n_mtiles + mt, ph = r & 1;
-      // epilogue warp slots 0..7 are warps 2..9; warp w owns quarter w & 3: slot -> quarter (slot + 2) & 3
-      int slot = -1;
-      for (int sl = 4 * ph; sl < 4 * ph + 4; ++sl)
-        if (((sl + 2) & 3) == q) slot = sl;
-      const long long pos = ((((long long)l * grid + c) * 8 + slot) * 32 + lane) * k + e;
-      const float v = cand_val[pos];
-      const int id = cand_idx[pos];
-      if (id >= 0 && (v > best || (v == best && id < best_id))) {
-        best = v; best_pos = pos; best_id = id;
+  const int ctas = grid / n_mtiles;                     // CTAs that worked on this row's batch tile
+  const int lists = ctas * 2;                           // two epilogue warps (column phases) per quarter
+  __shared__ float g_val[kTopkGather];
+  __shared__ int g_id[kTopkGather];
+  __shared__ int g_n;
+  __shared__ float s_val[8];
+  __shared__ int s_pos[8];
+  __shared__ int s_id[8];
+  unsigned int key = row_thr[b];
+  const float g = (key & 0x80000000u) ? __uint_as_float(key & 0x7FFFFFFFu) : __uint_as_float(~key);
+  if (threadIdx.x == 0) g_n = 0;
+  __syncthreads();
+  auto list_of = [&](int r) {
+    const int c = (r >> 1) * n_mtiles + mt, ph = r & 1;
+    // epilogue warp slots 0..7 are warps 2..9; warp w owns quarter w & 3: slot -> quarter (slot + 2) & 3
+    int slot = 4 * ph;
+    for (int sl = 4 * ph; sl < 4 * ph + 4; ++sl)
+      if (((sl + 2) & 3) == q) slot = sl;
+    return (c * 8 + slot) * 32 + lane;
+  };
+  for (int r = threadIdx.x; r < lists; r += blockDim.x) {
+    const int li = list_of(r);
+    const int n = list_cnt[li];
+    for (int e = 0; e < n; ++e) {
+      const float v = cand_val[(size_t)li * (cap + 32) + e];
+      if (v >= g) {
+        const int at = atomicAdd(&g_n, 1);
+        if (at < kTopkGather) {
+          g_val[at] = v;
+          g_id[at] = cand_idx[(size_t)li * (cap + 32) + e];
+        }
       }
     }
-    // block reduction
+  }
+  __syncthreads();
+  const int total = g_n;
+  const bool in_smem = total <= kTopkGather;
+  const int w = threadIdx.x >> 5, ln = threadIdx.x & 31;
+  for (int round = 0; round < k; ++round) {
+    float best = -INFINITY;
+    int best_pos = -1, best_id = 0x7fffffff;
+    if (in_smem) {
+      for (int t = threadIdx.x; t < total; t += blockDim.x) {
+        const float v = g_val[t];
+        const int id = g_id[t];
+        if (id >= 0 && (v > best || (v == best && id < best_id) || best_pos < 0)) { best = v; best_pos = t; best_id = id; }
+      }
+    } else {
+      for (int r = threadIdx.x; r < lists; r += blockDim.x) {
+        const int li = list_of(r);
+        const int n = list_cnt[li];
+        for (int e = 0; e < n; ++e) {
+          const float v = cand_val[(size_t)li * (cap + 32) + e];
+          const int id = cand_idx[(size_t)li * (cap + 32) + e];
+          if (id >= 0 && (v > best || (v == best && id < best_id) || best_pos < 0)) { best = v; best_pos = li * (cap + 32) + e; best_id = id; }
+        }
+      }
+    }
     for (int o = 16; o > 0; o >>= 1) {
       const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      const long long op = __shfl_xor_sync(0xffffffffu, best_pos, o);
+      const int op = __shfl_xor_sync(0xffffffffu, best_pos, o);
       const int oi = __shfl_xor_sync(0xffffffffu, best_id, o);
       if (op >= 0 && (best_pos < 0 || ov > best || (ov == best && oi < best_id))) { best = ov; best_pos = op; best_id = oi; }
     }
-    const int w = threadIdx.x >> 5, ln = threadIdx.x & 31;
     if (ln == 0) { s_val[w] = best; s_pos[w] = best_pos; s_id[w] = best_id; }
     __syncthreads();
     if (w == 0) {
@@ -277,14 +323,17 @@ __global__ void topk_merge_kernel(float* __restrict__ cand_val, int* __restrict_
       best_id = ln < nw ? s_id[ln] : 0x7fffffff;
       for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-        const long long op = __shfl_xor_sync(0xffffffffu, best_pos, o);
+        const int op = __shfl_xor_sync(0xffffffffu, best_pos, o);
         const int oi = __shfl_xor_sync(0xffffffffu, best_id, o);
         if (op >= 0 && (best_pos < 0 || ov > best || (ov == best && oi < best_id))) { best = ov; best_pos = op; best_id = oi; }
       }
       if (ln == 0) {
         out_val[(size_t)b * k + round] = best_pos >= 0 ? best : -INFINITY;
         out_idx[(size_t)b * k + round] = best_pos >= 0 ? (int)(label_offset + best_id) : -1;
-        if (best_pos >= 0) cand_idx[best_pos] = -1;                       // consumed
+        if (best_pos >= 0) {                                              // consumed
+          if (in_smem) g_id[best_pos] = -1;
+          else cand_idx[best_pos] = -1;
+        }
       }
     }
     __syncthreads();

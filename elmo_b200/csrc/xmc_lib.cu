@@ -194,6 +194,10 @@ struct xmc_handle {
   float* topk_val = nullptr;       // candidate lists of the fused top-k (grown on demand)
   int* topk_idx = nullptr;
   int64_t topk_cap = 0;            // entries
+  int* topk_cnt = nullptr;         // per list: entries in use
+  float* topk_thr = nullptr;       // per list: own threshold
+  unsigned int* topk_row = nullptr;  // per batch row: published threshold (ordered key)
+  int topk_lists = 0;
   void* kahan = nullptr;           // borrowed compensation buffer for the first kahan_rows rows
   int64_t kahan_rows = 0;
   int kahan_e5m2 = 0;
@@ -337,7 +341,7 @@ int xmc_destroy(xmc_handle* h) {
   if (h == nullptr) return XMC_OK;
   DeviceGuard guard(h->cfg.device);
   void* ptrs[] = {h->x8, h->x16, h->xt, h->G, h->w16, h->partial, h->bucket_cnt, h->bucket_off,
-                  h->entries, h->loss_partial, h->status, h->topk_val, h->topk_idx};
+                  h->entries, h->loss_partial, h->status, h->topk_val, h->topk_idx, h->topk_cnt, h->topk_thr, h->topk_row};
   for (void* p : ptrs)
     if (p != nullptr) cudaFree(p);
   for (cudaEvent_t e : h->ev_pool) cudaEventDestroy(e);
@@ -773,18 +777,30 @@ int xmc_forward_topk(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batc
   const int n_mt = cdiv(batch, 128);
   if (n_mt > h->sm_count) return fail(XMC_ERR_INVALID, "batch too large for the fused top-k");
   const int grid_max = h->sm_count / n_mt * n_mt;
-  const int spc = cdiv(h->rows_per_chunk, h->sched);
-  const int n_launch_max = (int)h->w_ptrs.size() * spc;
-  const int64_t need = (int64_t)n_launch_max * grid_max * 256 * k;
-  if (need > h->topk_cap) {
+  // candidate lists: one per (CTA, epilogue warp, lane), alive across the launches of this call
+  const int lists = grid_max * 256;
+  const int cap = k <= 16 ? 32 : (k <= 32 ? 64 : 256);
+  const int64_t need = (int64_t)lists * (cap + 32);
+  if (need > h->topk_cap || lists > h->topk_lists) {
     CU_TRY(cudaStreamSynchronize(st));
     if (h->topk_val) { cudaFree(h->topk_val); cudaFree(h->topk_idx); h->ws_bytes -= h->topk_cap * 8; h->topk_val = nullptr; h->topk_idx = nullptr; }
+    if (h->topk_cnt) { cudaFree(h->topk_cnt); cudaFree(h->topk_thr); h->ws_bytes -= (int64_t)h->topk_lists * 8; h->topk_cnt = nullptr; h->topk_thr = nullptr; }
     h->topk_cap = 0;
-    if (int rc = dev_alloc(h, (void**)&h->topk_val, (size_t)need * 4, false)) return rc;
-    if (int rc = dev_alloc(h, (void**)&h->topk_idx, (size_t)need * 4, false)) return rc;
-    h->topk_cap = need;
+    h->topk_lists = 0;
+    const int64_t cap_new = std::max<int64_t>(need, (int64_t)h->sm_count * 256 * (cap + 32));
+    const int lists_new = h->sm_count * 256;
+    if (int rc = dev_alloc(h, (void**)&h->topk_val, (size_t)cap_new * 4, false)) return rc;
+    if (int rc = dev_alloc(h, (void**)&h->topk_idx, (size_t)cap_new * 4, false)) return rc;
+    if (int rc = dev_alloc(h, (void**)&h->topk_cnt, (size_t)lists_new * 4, false)) return rc;
+    if (int rc = dev_alloc(h, (void**)&h->topk_thr, (size_t)lists_new * 4, false)) return rc;
+    h->topk_cap = cap_new;
+    h->topk_lists = lists_new;
   }
-  CU_TRY(cudaMemsetAsync(h->topk_idx, 0xFF, (size_t)need * 4, st));      // id -1: "no candidate"
+  if (h->topk_row == nullptr) {
+    if (int rc = dev_alloc(h, (void**)&h->topk_row, (size_t)std::max(h->bpad_max, 128) * 4, false)) return rc;
+  }
+  xmc::topk_init_kernel<<<cdiv(std::max(lists, batch), 256), 256, 0, st>>>(h->topk_cnt, h->topk_thr, lists, h->topk_row, batch);
+  CU_TRY(cudaGetLastError());
   if (int rc = prep_x(h, x, x_dtype, batch, bpad, fwd_fp8, !fwd_fp8, false, st)) return rc;
   CUtensorMap map_x;
   const size_t xrows = (size_t)std::max(h->bpad_max, 256);
@@ -823,26 +839,29 @@ int xmc_forward_topk(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batc
       tp.w_scale = h->cfg.w_scale;
       tp.col0 = row_base + s0;
       tp.n_out = n_out;
-      tp.cand_val = h->topk_val + (size_t)launch * grid_max * 256 * k;
-      tp.cand_idx = h->topk_idx + (size_t)launch * grid_max * 256 * k;
+      tp.cap = cap;
+      tp.cand_val = h->topk_val;
+      tp.cand_idx = h->topk_idx;
+      tp.list_cnt = h->topk_cnt;
+      tp.list_thr = h->topk_thr;
+      tp.row_thr = h->topk_row;
       tp.status = h->status;
       const int tiles = tp.n_mtiles * tp.n_ntiles;
-      const int grid = std::min(tiles, grid_max) / n_mt * n_mt;
+      // every launch uses the same grid, so that a list keeps its (CTA, warp, lane) owner; CTAs beyond
+      // the tile count find no work and leave their lists untouched
+      const int grid = grid_max;
       mark(h, K_LOGITS, st);
       int rc;
-#define XMC_TOPK(F8_, KM_) launch_gemm<xmc::TopkPolicy<F8_, KM_>>(map_x, map_w, tp, tiles, h->sm_count, st, grid)
-      if (k <= 8) rc = fwd_fp8 ? XMC_TOPK(true, 8) : XMC_TOPK(false, 8);
-      else if (k <= 32) rc = fwd_fp8 ? XMC_TOPK(true, 32) : XMC_TOPK(false, 32);
-      else rc = fwd_fp8 ? XMC_TOPK(true, 128) : XMC_TOPK(false, 128);
-#undef XMC_TOPK
+      rc = fwd_fp8 ? launch_gemm<xmc::TopkPolicy<true>>(map_x, map_w, tp, tiles, h->sm_count, st, grid)
+                   : launch_gemm<xmc::TopkPolicy<false>>(map_x, map_w, tp, tiles, h->sm_count, st, grid);
       if (rc) return rc;
       ++launch;
     }
     row_base += rows_wc;
   }
   mark(h, K_LOGITS, st);
-  xmc::topk_merge_kernel<<<batch, 256, 0, st>>>(h->topk_val, h->topk_idx, launch, grid_max, n_mt, k, batch,
-                                                h->cfg.label_offset, vals, idx);
+  xmc::topk_merge_kernel<<<batch, 256, 0, st>>>(h->topk_val, h->topk_idx, h->topk_cnt, h->topk_row, cap, grid_max, n_mt, k,
+                                                batch, h->cfg.label_offset, vals, idx);
   CU_TRY(cudaGetLastError());
   mark(h, K_END, st);
   return XMC_OK;

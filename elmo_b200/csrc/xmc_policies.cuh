@@ -527,16 +527,35 @@ struct TopkParams {
   int batch, rows;
   int n_mtiles, n_ntiles;
   int k_steps;
-  int k;
+  int k, cap;              // wanted entries per row; capacity of one candidate list (> k)
   float w_scale;
   long long col0;          // index (within the handle) of this launch's label row 0
   long long n_out;         // rows >= n_out are ignored (padding)
-  float* cand_val;         // [gridDim.x * 256 threads][k]
+  float* cand_val;         // [lists][cap + 32], list = (CTA * 8 + epilogue warp) * 32 + lane; lists live across launches
   int* cand_idx;
+  int* list_cnt;           // [lists] entries in use
+  float* list_thr;         // [lists] value a new candidate of this list must exceed
+  unsigned int* row_thr;   // [batch rows] ordered key of the best k-th value any list of the row has published
   int* status;
 };
 
-template <bool FP8, int KMAX>
+// monotone map float -> unsigned (larger float = larger key), and back
+__device__ __forceinline__ unsigned int topk_key(float v) {
+  const unsigned int b = __float_as_uint(v);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float topk_unkey(unsigned int k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7FFFFFFFu) : ~k);
+}
+
+// A thread owns one batch row of its CTA's batch tile and keeps an UNSORTED candidate list in global
+// memory: a logit joins it when it beats the list's own threshold (strictly: later labels of a list
+// have higher ids and lose ties) and reaches the row's published threshold (the best k-th value any
+// list of that row has seen: nothing below it can be in the row's top-k).  A full list is cut back to
+// its k best by a radix select, which raises both thresholds.  Appending is a few instructions, so the
+// divergence of 32 lanes with 32 different rows stays cheap, and because all lists of a row share the
+// published threshold the number of candidates per row stays near k ln(L/k) however many CTAs there are.
+template <bool FP8>
 struct TopkPolicy {
   using Params = TopkParams;
   static constexpr bool kMnMajor = false;
@@ -545,9 +564,10 @@ struct TopkPolicy {
   static constexpr int kElemsPerRow = FP8 ? 128 : 64;
   static constexpr int kEpiWarps = 8;
   struct EpilogueState {
-    float val[KMAX];       // descending
-    int idx[KMAX];
-    float thr;             // val[k-1]
+    float thr;             // own threshold
+    float g;               // published threshold of the row (refreshed per tile)
+    int cnt;
+    int list;              // -1 until the first tile
   };
   __device__ static int num_tiles(const Params& p) { return p.n_mtiles * p.n_ntiles; }
   __device__ static void job(const Params& p, int tile, Job& j) {
@@ -559,17 +579,66 @@ struct TopkPolicy {
     j.k_steps = p.k_steps;
     j.n_eff = min(kTileN, round_up16(p.rows - j.b0));
   }
-  __device__ static void epilogue_begin(const Params& p, EpilogueState& st) {
-    for (int i = 0; i < p.k; ++i) {
-      st.val[i] = -INFINITY;
-      st.idx[i] = -1;
+  __device__ static void epilogue_begin(const Params&, EpilogueState& st) { st.list = -1; }
+  __device__ static void epilogue_pre(const Params& p, const Job& j, SharedTail&, const EpiCtx& ec, EpilogueState& st) {
+    if (st.list < 0) {
+      st.list = ((int)blockIdx.x * kEpiWarps + ec.slot) * 32 + ec.lane;
+      st.cnt = p.list_cnt[st.list];
+      st.thr = p.list_thr[st.list];
     }
-    st.thr = -INFINITY;
+    const int b = j.a0 + ec.q * 32 + ec.lane;
+    st.g = b < p.batch ? topk_unkey(__ldcg(&p.row_thr[b])) : INFINITY;
   }
-  __device__ static void epilogue_pre(const Params&, const Job&, SharedTail&, const EpiCtx&, EpilogueState&) {}
+  // The whole warp cuts one list of n entries back to its k best (ties: first come = lower id): a radix
+  // select over the ordered keys with one warp-wide count per bit, then a stable compaction.  Returns
+  // the new threshold (the k-th largest value) to every lane and publishes it for row b.
+  __device__ __noinline__ static float prune_warp(const Params& p, int list, int n, int b, int lane) {
+    float* val = p.cand_val + (size_t)list * kListStride(p);
+    int* idx = p.cand_idx + (size_t)list * kListStride(p);
+    unsigned int prefix = 0u, mask = 0u;
+    int need = p.k;                                  // rank still wanted among the entries matching the prefix
+    for (int bit = 31; bit >= 0; --bit) {
+      const unsigned int bm = 1u << bit;
+      int c = 0;
+      for (int e = lane; e < n; e += 32) c += ((topk_key(val[e]) & (mask | bm)) == (prefix | bm)) ? 1 : 0;
+      c = __reduce_add_sync(0xffffffffu, c);
+      if (c >= need) prefix |= bm;
+      else need -= c;
+      mask |= bm;
+    }
+    const float t = topk_unkey(prefix);              // `need` entries equal to it survive
+    int w = 0, eq = 0;
+    const unsigned int lt = (1u << lane) - 1u;
+    for (int e0 = 0; e0 < n; e0 += 32) {
+      const int e = e0 + lane;
+      const float v = e < n ? val[e] : -INFINITY;
+      const int id = e < n ? idx[e] : -1;
+      const bool is_eq = e < n && v == t;
+      const unsigned int eqm = __ballot_sync(0xffffffffu, is_eq);
+      const bool keep = e < n && (v > t || (is_eq && eq + __popc(eqm & lt) < need));
+      const unsigned int km = __ballot_sync(0xffffffffu, keep);
+      __syncwarp();                                  // every lane holds its entry before any slot is rewritten
+      if (keep) {
+        const int pos = w + __popc(km & lt);
+        val[pos] = v;
+        idx[pos] = id;
+      }
+      w += __popc(km);
+      eq += __popc(eqm);
+      __syncwarp();
+    }
+    if (lane == 0) atomicMax(&p.row_thr[b], prefix);
+    return t;
+  }
+  __device__ static int kListStride(const Params& p) { return p.cap + 32; }   // a group may overshoot cap by 31
   __device__ static void epilogue(const Params& p, const Job& j, uint32_t taddr, bool have_acc,
                                   SharedTail&, const EpiCtx& ec, EpilogueState& st) {
     const int b = j.a0 + ec.q * 32 + ec.lane;
+    const bool active = b < p.batch;
+    float* val = p.cand_val + (size_t)st.list * kListStride(p);
+    int* idx = p.cand_idx + (size_t)st.list * kListStride(p);
+    float thr = st.thr, g = st.g;
+    int cnt = st.cnt;
     for (int c0 = 32 * ec.h; c0 < j.n_eff; c0 += 32 * ec.nsplit) {
       uint32_t v[32];
       if (have_acc) {
@@ -579,32 +648,57 @@ struct TopkPolicy {
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = 0u;
       }
-      if (b >= p.batch) continue;
       const long long col = p.col0 + j.b0 + c0;
       const int valid = (int)max(0ll, min(32ll, min((long long)(p.rows - j.b0 - c0), p.n_out - col)));
+      // pass 1, branch-free: which of the 32 logits reach the thresholds as they stand now
+      const float lim = fmaxf(thr, g);
+      uint32_t hit = 0u;
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
         const float z = bf16_round(__uint_as_float(v[i]) * p.w_scale);
-        if (i < valid && z > st.thr) {            // labels arrive in ascending order: ties keep the lower id
-          int pos = p.k - 1;
-          while (pos > 0 && st.val[pos - 1] < z) {
-            st.val[pos] = st.val[pos - 1];
-            st.idx[pos] = st.idx[pos - 1];
-            --pos;
+        v[i] = __float_as_uint(z);
+        hit |= (z >= lim ? 1u : 0u) << i;
+      }
+      hit &= valid >= 32 ? 0xFFFFFFFFu : ((1u << valid) - 1u);
+      if (!active) hit = 0u;
+      if (!__any_sync(0xffffffffu, hit != 0u)) continue;          // warp-uniform
+      // pass 2, rare: append in label order (own threshold strict: later labels lose ties)
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        if (hit & (1u << i)) {
+          const float z = __uint_as_float(v[i]);
+          if (z > thr && z >= g) {
+            val[cnt] = z;
+            idx[cnt] = (int)(col + i);
+            ++cnt;
           }
-          st.val[pos] = z;
-          st.idx[pos] = (int)(col + i);
-          st.thr = st.val[p.k - 1];
+        }
+      }
+      __syncwarp();
+      // full lists are cut back by the whole warp, one list at a time
+      unsigned int full = __ballot_sync(0xffffffffu, cnt >= p.cap);
+      while (full) {
+        const int src = __ffs(full) - 1;
+        full &= full - 1u;
+        const int l_src = __shfl_sync(0xffffffffu, st.list, src);
+        const int n_src = __shfl_sync(0xffffffffu, cnt, src);
+        const int b_src = __shfl_sync(0xffffffffu, b, src);
+        const float t = prune_warp(p, l_src, n_src, b_src, ec.lane);
+        if (ec.lane == src) {
+          thr = t;
+          cnt = p.k;
+          g = fmaxf(g, t);
         }
       }
     }
+    st.thr = thr;
+    st.g = g;
+    st.cnt = cnt;
   }
-  __device__ static void epilogue_end(const Params& p, SharedTail&, const EpiCtx& ec, EpilogueState& st) {
-    const size_t base = ((size_t)blockIdx.x * (kEpiWarps * 32) + ec.slot * 32 + ec.lane) * p.k;
-    for (int i = 0; i < p.k; ++i) {
-      p.cand_val[base + i] = st.val[i];
-      p.cand_idx[base + i] = st.idx[i];
-    }
+  __device__ static void epilogue_end(const Params& p, SharedTail&, const EpiCtx&, EpilogueState& st) {
+    if (st.list < 0) return;                          // this CTA had no tile
+    p.list_cnt[st.list] = st.cnt;
+    p.list_thr[st.list] = st.thr;
   }
 };
 
