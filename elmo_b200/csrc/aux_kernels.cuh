@@ -226,12 +226,14 @@ __global__ void reduce_gradx_kernel(const float* __restrict__ partial, int n_spl
 }
 
 // State of the fused top-k before its first launch: empty lists, thresholds at -inf.
-__global__ void topk_init_kernel(int* __restrict__ list_cnt, float* __restrict__ list_thr, int lists,
+__global__ void topk_init_kernel(int* __restrict__ list_cnt, float* __restrict__ list_thr,
+                                 float* __restrict__ list_max, int lists,
                                  unsigned int* __restrict__ row_thr, int rows) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < lists) {
     list_cnt[i] = 0;
     list_thr[i] = -INFINITY;
+    list_max[i] = -INFINITY;
   }
   if (i < rows) row_thr[i] = 0x007FFFFFu;                // ordered key of -inf
 }

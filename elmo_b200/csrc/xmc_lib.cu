@@ -196,6 +196,7 @@ struct xmc_handle {
   int64_t topk_cap = 0;            // entries
   int* topk_cnt = nullptr;         // per list: entries in use
   float* topk_thr = nullptr;       // per list: own threshold
+  float* topk_max = nullptr;       // per list: largest value held so far
   unsigned int* topk_row = nullptr;  // per batch row: published threshold (ordered key)
   int topk_lists = 0;
   void* kahan = nullptr;           // borrowed compensation buffer for the first kahan_rows rows
@@ -341,7 +342,7 @@ int xmc_destroy(xmc_handle* h) {
   if (h == nullptr) return XMC_OK;
   DeviceGuard guard(h->cfg.device);
   void* ptrs[] = {h->x8, h->x16, h->xt, h->G, h->w16, h->partial, h->bucket_cnt, h->bucket_off,
-                  h->entries, h->loss_partial, h->status, h->topk_val, h->topk_idx, h->topk_cnt, h->topk_thr, h->topk_row};
+                  h->entries, h->loss_partial, h->status, h->topk_val, h->topk_idx, h->topk_cnt, h->topk_thr, h->topk_max, h->topk_row};
   for (void* p : ptrs)
     if (p != nullptr) cudaFree(p);
   for (cudaEvent_t e : h->ev_pool) cudaEventDestroy(e);
@@ -779,12 +780,12 @@ int xmc_forward_topk(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batc
   const int grid_max = h->sm_count / n_mt * n_mt;
   // candidate lists: one per (CTA, epilogue warp, lane), alive across the launches of this call
   const int lists = grid_max * 256;
-  const int cap = k <= 16 ? 32 : (k <= 32 ? 64 : 256);
+  const int cap = k <= 16 ? 96 : (k <= 32 ? 128 : 256);
   const int64_t need = (int64_t)lists * (cap + 32);
   if (need > h->topk_cap || lists > h->topk_lists) {
     CU_TRY(cudaStreamSynchronize(st));
     if (h->topk_val) { cudaFree(h->topk_val); cudaFree(h->topk_idx); h->ws_bytes -= h->topk_cap * 8; h->topk_val = nullptr; h->topk_idx = nullptr; }
-    if (h->topk_cnt) { cudaFree(h->topk_cnt); cudaFree(h->topk_thr); h->ws_bytes -= (int64_t)h->topk_lists * 8; h->topk_cnt = nullptr; h->topk_thr = nullptr; }
+    if (h->topk_cnt) { cudaFree(h->topk_cnt); cudaFree(h->topk_thr); cudaFree(h->topk_max); h->ws_bytes -= (int64_t)h->topk_lists * 12; h->topk_cnt = nullptr; h->topk_thr = nullptr; h->topk_max = nullptr; }
     h->topk_cap = 0;
     h->topk_lists = 0;
     const int64_t cap_new = std::max<int64_t>(need, (int64_t)h->sm_count * 256 * (cap + 32));
@@ -793,13 +794,14 @@ int xmc_forward_topk(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batc
     if (int rc = dev_alloc(h, (void**)&h->topk_idx, (size_t)cap_new * 4, false)) return rc;
     if (int rc = dev_alloc(h, (void**)&h->topk_cnt, (size_t)lists_new * 4, false)) return rc;
     if (int rc = dev_alloc(h, (void**)&h->topk_thr, (size_t)lists_new * 4, false)) return rc;
+    if (int rc = dev_alloc(h, (void**)&h->topk_max, (size_t)lists_new * 4, false)) return rc;
     h->topk_cap = cap_new;
     h->topk_lists = lists_new;
   }
   if (h->topk_row == nullptr) {
     if (int rc = dev_alloc(h, (void**)&h->topk_row, (size_t)std::max(h->bpad_max, 128) * 4, false)) return rc;
   }
-  xmc::topk_init_kernel<<<cdiv(std::max(lists, batch), 256), 256, 0, st>>>(h->topk_cnt, h->topk_thr, lists, h->topk_row, batch);
+  xmc::topk_init_kernel<<<cdiv(std::max(lists, batch), 256), 256, 0, st>>>(h->topk_cnt, h->topk_thr, h->topk_max, lists, h->topk_row, batch);
   CU_TRY(cudaGetLastError());
   if (int rc = prep_x(h, x, x_dtype, batch, bpad, fwd_fp8, !fwd_fp8, false, st)) return rc;
   CUtensorMap map_x;
@@ -844,6 +846,7 @@ int xmc_forward_topk(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batc
       tp.cand_idx = h->topk_idx;
       tp.list_cnt = h->topk_cnt;
       tp.list_thr = h->topk_thr;
+      tp.list_max = h->topk_max;
       tp.row_thr = h->topk_row;
       tp.status = h->status;
       const int tiles = tp.n_mtiles * tp.n_ntiles;

@@ -535,6 +535,7 @@ struct TopkParams {
   int* cand_idx;
   int* list_cnt;           // [lists] entries in use
   float* list_thr;         // [lists] value a new candidate of this list must exceed
+  float* list_max;         // [lists] largest value the list has ever held
   unsigned int* row_thr;   // [batch rows] ordered key of the best k-th value any list of the row has published
   int* status;
 };
@@ -568,6 +569,7 @@ struct TopkPolicy {
     float g;               // published threshold of the row (refreshed per tile)
     int cnt;
     int list;              // -1 until the first tile
+    float mx;              // largest value appended so far
   };
   __device__ static int num_tiles(const Params& p) { return p.n_mtiles * p.n_ntiles; }
   __device__ static void job(const Params& p, int tile, Job& j) {
@@ -581,12 +583,38 @@ struct TopkPolicy {
   }
   __device__ static void epilogue_begin(const Params&, EpilogueState& st) { st.list = -1; }
   __device__ static void epilogue_pre(const Params& p, const Job& j, SharedTail&, const EpiCtx& ec, EpilogueState& st) {
+    const int b = j.a0 + ec.q * 32 + ec.lane;
     if (st.list < 0) {
       st.list = ((int)blockIdx.x * kEpiWarps + ec.slot) * 32 + ec.lane;
       st.cnt = p.list_cnt[st.list];
       st.thr = p.list_thr[st.list];
+      st.mx = p.list_max[st.list];
+      // Once per launch and row (first CTA of the batch tile, first column phase): the k-th largest of
+      // the best values of the row's lists is reached by k different labels, so nothing below it can be
+      // among the row's k best.  This is far tighter than any single list's own k-th value.
+      const int lists_row = ((int)gridDim.x / p.n_mtiles) * 2;
+      if ((int)blockIdx.x < p.n_mtiles && ec.h == 0 && b < p.batch && p.k <= 8 && lists_row >= p.k) {
+        float top[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) top[i] = -INFINITY;
+        for (int r = 0; r < lists_row; ++r) {
+          const int c = (r >> 1) * p.n_mtiles + (int)blockIdx.x;
+          // the epilogue warp of column phase (r & 1) that owns this thread's TMEM quarter
+          const int slot = 4 * (r & 1) + ((ec.q + 2) & 3);
+          float x = __ldcg(&p.list_max[(c * kEpiWarps + slot) * 32 + ec.lane]);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {             // insertion into the descending array
+            const float hi = fmaxf(top[i], x);
+            x = fminf(top[i], x);
+            top[i] = hi;
+          }
+        }
+        float kth = top[0];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) kth = (i < p.k) ? top[i] : kth;
+        atomicMax(&p.row_thr[b], topk_key(kth));
+      }
     }
-    const int b = j.a0 + ec.q * 32 + ec.lane;
     st.g = b < p.batch ? topk_unkey(__ldcg(&p.row_thr[b])) : INFINITY;
   }
   // The whole warp cuts one list of n entries back to its k best (ties: first come = lower id): a radix
@@ -595,6 +623,46 @@ struct TopkPolicy {
   __device__ __noinline__ static float prune_warp(const Params& p, int list, int n, int b, int lane) {
     float* val = p.cand_val + (size_t)list * kListStride(p);
     int* idx = p.cand_idx + (size_t)list * kListStride(p);
+    const unsigned int lt = (1u << lane) - 1u;
+    if (p.k <= 16 && n <= 128) {
+      // few wanted, few held: k rounds of "largest remaining entry, earliest first", four entries per lane
+      unsigned int key[4];
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) key[jj] = (lane + 32 * jj < n) ? topk_key(val[lane + 32 * jj]) : 0u;
+      unsigned int taken = 0u, t_key = 0u;
+      for (int r = 0; r < p.k; ++r) {
+        unsigned int m = 0u;
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) m = ((taken >> jj) & 1u) ? m : max(m, key[jj]);
+        m = __reduce_max_sync(0xffffffffu, m);
+        int e_mine = 0x7fffffff;
+#pragma unroll
+        for (int jj = 3; jj >= 0; --jj)
+          if (!((taken >> jj) & 1u) && key[jj] == m) e_mine = lane + 32 * jj;
+        const int e_min = __reduce_min_sync(0xffffffffu, e_mine);
+        if ((e_min & 31) == lane) taken |= 1u << (e_min >> 5);
+        t_key = m;
+      }
+      int w = 0;
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        const int e = lane + 32 * jj;
+        const bool keep = (taken >> jj) & 1u;
+        const float v = keep ? val[e] : 0.f;
+        const int id = keep ? idx[e] : 0;
+        const unsigned int km = __ballot_sync(0xffffffffu, keep);
+        __syncwarp();
+        if (keep) {
+          const int pos = w + __popc(km & lt);
+          val[pos] = v;
+          idx[pos] = id;
+        }
+        w += __popc(km);
+        __syncwarp();
+      }
+      if (lane == 0) atomicMax(&p.row_thr[b], t_key);
+      return topk_unkey(t_key);
+    }
     unsigned int prefix = 0u, mask = 0u;
     int need = p.k;                                  // rank still wanted among the entries matching the prefix
     for (int bit = 31; bit >= 0; --bit) {
@@ -608,7 +676,6 @@ struct TopkPolicy {
     }
     const float t = topk_unkey(prefix);              // `need` entries equal to it survive
     int w = 0, eq = 0;
-    const unsigned int lt = (1u << lane) - 1u;
     for (int e0 = 0; e0 < n; e0 += 32) {
       const int e = e0 + lane;
       const float v = e < n ? val[e] : -INFINITY;
@@ -637,7 +704,7 @@ struct TopkPolicy {
     const bool active = b < p.batch;
     float* val = p.cand_val + (size_t)st.list * kListStride(p);
     int* idx = p.cand_idx + (size_t)st.list * kListStride(p);
-    float thr = st.thr, g = st.g;
+    float thr = st.thr, g = st.g, mx = st.mx;
     int cnt = st.cnt;
     for (int c0 = 32 * ec.h; c0 < j.n_eff; c0 += 32 * ec.nsplit) {
       uint32_t v[32];
@@ -671,6 +738,7 @@ struct TopkPolicy {
             val[cnt] = z;
             idx[cnt] = (int)(col + i);
             ++cnt;
+            mx = fmaxf(mx, z);
           }
         }
       }
@@ -694,11 +762,13 @@ struct TopkPolicy {
     st.thr = thr;
     st.g = g;
     st.cnt = cnt;
+    st.mx = mx;
   }
   __device__ static void epilogue_end(const Params& p, SharedTail&, const EpiCtx&, EpilogueState& st) {
     if (st.list < 0) return;                          // this CTA had no tile
     p.list_cnt[st.list] = st.cnt;
     p.list_thr[st.list] = st.thr;
+    p.list_max[st.list] = st.mx;
   }
 };
 
