@@ -57,3 +57,26 @@ def test_topk_ties_take_lower_id_and_bf16_class():
     layer._handle.check()
     assert idx.cpu().tolist() == [[500, 7, 300, 999]] * B
     assert vals.cpu().tolist() == [[3.0, 2.0, 2.0, 2.0]] * B
+
+
+@pytest.mark.parametrize("k", [5, 40])
+def test_topk_all_logits_equal_keeps_the_lowest_ids(k):
+    """Every label ties with every other one across all CTAs, lists and launches: the published row
+    threshold must not drop a lower id that arrives in another list."""
+    from elmo_b200.handle import XmcHandle
+    L, d, B = 40000, 64, 130
+    dev = torch.device("cuda", 0)
+    w = torch.zeros(L, d, dtype=torch.bfloat16)
+    w[:, 0] = 1.5
+    w[L // 2 + 11, 0] = 2.5                                                # one clear winner in the second chunk
+    chunks = [w[:L // 2].contiguous().to(dev), w[L // 2:].contiguous().to(dev)]
+    x = torch.zeros(B, d, dtype=torch.bfloat16)
+    x[:, 0] = 1.0
+    h = XmcHandle(dev, d, B, "bf16", sched_labels=4096)
+    h.bind(chunks)
+    vals, idx = h.forward_topk(x.to(dev), k, L)
+    h.check()
+    want = [L // 2 + 11] + list(range(k - 1))
+    assert idx.cpu().tolist() == [want] * B
+    assert vals.cpu()[:, 0].tolist() == [2.5] * B and bool((vals.cpu()[:, 1:] == 1.5).all())
+    h.close()
