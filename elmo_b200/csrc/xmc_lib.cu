@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -55,6 +56,27 @@ int get_encode(EncodeFn* out) {
   return XMC_OK;
 }
 
+// Encoding a tensor map costs a few microseconds on the host and a step needs ~26 of them with
+// arguments that repeat every step, so encoded maps are remembered (per thread, direct-mapped).
+struct MapKey {
+  uint64_t base, a, b, c;
+  uint32_t kind, e4m3, box0, box1, swizzle, pad;
+  bool operator==(const MapKey& o) const { return memcmp(this, &o, sizeof(MapKey)) == 0; }
+};
+struct MapSlot {
+  MapKey key;
+  CUtensorMap map;
+  bool used = false;
+};
+constexpr int kMapSlots = 512;
+inline MapSlot* map_slot(const MapKey& k) {
+  static thread_local MapSlot slots[kMapSlots];
+  uint64_t h = k.base * 0x9E3779B97F4A7C15ull ^ (k.a * 0xC2B2AE3D27D4EB4Full) ^ (k.b << 17) ^ (k.c << 3) ^
+               ((uint64_t)k.kind << 60) ^ ((uint64_t)k.box1 << 40) ^ ((uint64_t)k.box0 << 50) ^ k.e4m3 ^ ((uint64_t)k.swizzle << 1);
+  h ^= h >> 29;
+  return &slots[h % kMapSlots];
+}
+
 // 2-D row-major tensor [outer x inner], box [box_outer x box_inner], 128-byte swizzle, zero fill.
 int make_map(CUtensorMap* m, bool e4m3, const void* base, uint64_t inner, uint64_t outer,
              uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, bool swizzle = true) {
@@ -63,6 +85,15 @@ int make_map(CUtensorMap* m, bool e4m3, const void* base, uint64_t inner, uint64
   if (((uintptr_t)base & 15u) != 0 || (row_stride_bytes & 15u) != 0)
     return fail(XMC_ERR_INVALID, "tensor base/stride must be 16-byte aligned (base %p, stride %llu)", base,
                 (unsigned long long)row_stride_bytes);
+  MapKey key;
+  memset(&key, 0, sizeof(key));
+  key.base = (uint64_t)(uintptr_t)base; key.a = inner; key.b = outer; key.c = row_stride_bytes;
+  key.kind = 2; key.e4m3 = e4m3; key.box0 = box_inner; key.box1 = box_outer; key.swizzle = swizzle;
+  MapSlot* slot = map_slot(key);
+  if (slot->used && slot->key == key) {
+    *m = slot->map;
+    return XMC_OK;
+  }
   const cuuint64_t dims[2] = {inner, outer};
   const cuuint64_t strides[1] = {row_stride_bytes};
   const cuuint32_t box[2] = {box_inner, box_outer};
@@ -76,6 +107,9 @@ int make_map(CUtensorMap* m, bool e4m3, const void* base, uint64_t inner, uint64
     return fail(XMC_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d): inner %llu outer %llu stride %llu box %ux%u",
                 (int)r, (unsigned long long)inner, (unsigned long long)outer,
                 (unsigned long long)row_stride_bytes, box_inner, box_outer);
+  slot->key = key;
+  slot->map = *m;
+  slot->used = true;
   return XMC_OK;
 }
 // [rows x cols] row-major matrix seen as [cols/64 blocks][rows][64 elements]: one box fetches
@@ -89,6 +123,15 @@ int make_map_blocked(CUtensorMap* m, bool e4m3, const void* base, uint64_t cols,
   if (cols % 64 != 0) return fail(XMC_ERR_INVALID, "blocked tensor map needs a multiple of 64 columns, got %llu", (unsigned long long)cols);
   if (((uintptr_t)base & 15u) != 0 || ((row_stride_elems * es) & 15u) != 0)
     return fail(XMC_ERR_INVALID, "tensor base/stride must be 16-byte aligned");
+  MapKey key;
+  memset(&key, 0, sizeof(key));
+  key.base = (uint64_t)(uintptr_t)base; key.a = cols; key.b = rows; key.c = row_stride_elems;
+  key.kind = 3; key.e4m3 = e4m3; key.box0 = 64; key.box1 = box_rows; key.swizzle = swizzle;
+  MapSlot* slot = map_slot(key);
+  if (slot->used && slot->key == key) {
+    *m = slot->map;
+    return XMC_OK;
+  }
   const cuuint64_t dims[3] = {64, rows, cols / 64};
   const cuuint64_t strides[2] = {row_stride_elems * es, 64ull * es};
   const cuuint32_t box[3] = {64, box_rows, 4};
@@ -100,6 +143,9 @@ int make_map_blocked(CUtensorMap* m, bool e4m3, const void* base, uint64_t cols,
   if (r != CUDA_SUCCESS)
     return fail(XMC_ERR_CUDA, "cuTensorMapEncodeTiled (blocked) failed (%d): cols %llu rows %llu stride %llu",
                 (int)r, (unsigned long long)cols, (unsigned long long)rows, (unsigned long long)row_stride_elems);
+  slot->key = key;
+  slot->map = *m;
+  slot->used = true;
   return XMC_OK;
 }
 // operand whose K runs along the rows' contiguous direction
@@ -133,13 +179,32 @@ cudaError_t launch_pdl(Kern kern, int grid, int block, size_t smem, cudaStream_t
   return cudaLaunchKernelEx(&cfg, kern, args...);
 }
 
+// dynamic shared memory opt-in of the grad_X kernels, once per device
+int gradx_configure() {
+  static std::atomic<uint64_t> configured{0};
+  int dev = 0;
+  CU_TRY(cudaGetDevice(&dev));
+  if (!((configured.load(std::memory_order_relaxed) >> (dev & 63)) & 1ull)) {
+    CU_TRY(cudaFuncSetAttribute(xmc::gradx_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, xmc::kGxSmemBytes));
+    CU_TRY(cudaFuncSetAttribute(xmc::gradx_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, xmc::kGxSmemBytes));
+    configured.fetch_or(1ull << (dev & 63));
+  }
+  return XMC_OK;
+}
+
 template <class Policy>
 int launch_gemm(const CUtensorMap& a, const CUtensorMap& b, const typename Policy::Params& p, int n_tiles,
                 int sm_count, cudaStream_t stream, int grid_override = 0) {
   if (n_tiles <= 0) return XMC_OK;
   auto kern = xmc::gemm_kernel<Policy>;
-  // per device and cheap; one process may drive several devices
-  CU_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, xmc::kSmemBytes));
+  // once per device and kernel (one process may drive several devices)
+  static std::atomic<uint64_t> configured{0};
+  int dev = 0;
+  CU_TRY(cudaGetDevice(&dev));
+  if (!((configured.load(std::memory_order_relaxed) >> (dev & 63)) & 1ull)) {
+    CU_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, xmc::kSmemBytes));
+    configured.fetch_or(1ull << (dev & 63));
+  }
   const int grid = grid_override > 0 ? grid_override : std::min(n_tiles, sm_count);
   CU_TRY(launch_pdl(kern, grid, 64 + 32 * Policy::kEpiWarps, xmc::kSmemBytes, stream, a, b, p));
   return XMC_OK;
@@ -600,10 +665,10 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
       {
         const int grid = n_bt * n_dt * n_splits;
         if (w8) {
-          CU_TRY(cudaFuncSetAttribute(xmc::gradx_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, xmc::kGxSmemBytes));
+          if (int rc2 = gradx_configure()) return rc2;
           CU_TRY(launch_pdl(xmc::gradx_kernel<true>, grid, xmc::kGxThreads, xmc::kGxSmemBytes, st, map_g_mn, map_w_gx, gp));
         } else {
-          CU_TRY(cudaFuncSetAttribute(xmc::gradx_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, xmc::kGxSmemBytes));
+          if (int rc2 = gradx_configure()) return rc2;
           CU_TRY(launch_pdl(xmc::gradx_kernel<false>, grid, xmc::kGxThreads, xmc::kGxSmemBytes, st, map_g_mn, map_w_gx, gp));
         }
         CU_TRY(cudaGetLastError());
