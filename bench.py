@@ -10,7 +10,8 @@ contiguous label ranges, data-parallel batch of 512 per rank (global batch 512 N
 grad_X reduce-scattered: per-GPU work is constant, so scaling is "weak".
 
 One "step" is one ``xfc_forward_backward``.  ``value`` is measured with the inputs resident on the
-device; ``e2e`` feeds pinned host buffers and reads the activation gradient back every step.
+device; ``e2e`` feeds pinned host buffers and reads the activation gradient back every step (the host
+waits for the previous step's read-back, so one step is in flight while the next is queued).
 ``--impl reference`` times the CPU restatement of the reference's step (oracle/) on a bounded
 sample of the same workload with all host threads.
 """
@@ -260,17 +261,26 @@ def run_ours(args, wl, rank, local_rank, world):
         grad_of = lambda: layer.grad_input
     dev_pool = [(x.to(device), l.to(device)) for x, l in pool]
     pin_pool = [(x.pin_memory(), l.pin_memory()) for x, l in pool]
-    host_grad = torch.empty(b_loc, wl.dim, dtype=torch.bfloat16).pin_memory()
+    host_grad = [torch.empty(b_loc, wl.dim, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    read_done = [torch.cuda.Event(), torch.cuda.Event()]
+    e2e_state = {"prev": -1}
 
     def step_resident(i):
         x, lab = dev_pool[i % n_pool]
         step_fn(x, lab)
 
     def step_e2e(i):
+        # every step: inputs come from pinned host memory, the activation gradient goes back to pinned
+        # host memory.  The host waits for the PREVIOUS step's read-back while this step is already
+        # queued (two host buffers), as a training loop that consumes the result one step later would.
         x, lab = pin_pool[i % n_pool]
         step_fn(x.to(device, non_blocking=True), lab.to(device, non_blocking=True))
-        host_grad.copy_(grad_of(), non_blocking=True)
-        torch.cuda.current_stream(device).synchronize()
+        s = i & 1
+        host_grad[s].copy_(grad_of(), non_blocking=True)
+        read_done[s].record(torch.cuda.current_stream(device))
+        if e2e_state["prev"] >= 0:
+            read_done[e2e_state["prev"]].synchronize()
+        e2e_state["prev"] = s
 
     torch.cuda.reset_peak_memory_stats(device)
     l0 = handle.launch_count
@@ -326,7 +336,7 @@ def run_ours(args, wl, rank, local_rank, world):
         "clocks": clk.summary(),
         "e2e": {"value": B * args.steps / (ms_e2e * 1e-3), "unit": UNIT,
                 "h2d_bytes_per_step": int(sum(x.numel() * 2 + l.numel() * 4 for x, l in pool) / n_pool),
-                "d2h_bytes_per_step": int(host_grad.numel() * 2)},
+                "d2h_bytes_per_step": int(host_grad[0].numel() * 2)},
         "gpu_launches": int(launches),
         "roofline": {"bound": "tensor", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                      "frac": achieved / peak, "traffic": traffic,
