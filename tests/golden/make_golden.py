@@ -21,7 +21,9 @@ import numpy as np
 import torch
 
 os.environ.setdefault("TORCHDYNAMO_DISABLE", "1")
-ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: make_golden.py /path/to/reference")
+ref_root = sys.argv[1]
 sys.path.insert(0, os.path.join(ref_root, "src"))
 here = os.path.dirname(os.path.abspath(__file__))
 
