@@ -2,6 +2,7 @@
 """Benchmark of the chunked XMC classifier layer train step (samples/s).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg2]
+    python bench.py --pass topk [--topk 5]        # the fused top-k inference pass, one GPU
 
 N = 1: the FP8 chunked step the headline metric is quoted on (670 091 labels x 768, batch 512,
 e4m3 weights, stochastic rounding, skip-loss), through ``Fp8XMCBCEChunkedLayer``.
@@ -354,6 +355,43 @@ def run_ours(args, wl, rank, local_rank, world):
     print(json.dumps(out))
 
 
+def run_topk(args, wl):
+    """``--pass topk``: the fused logits + top-k inference pass over the same layer (single GPU, one
+    line of its own; the default run never comes here)."""
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (sm_100a); there is no CPU fallback"
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    from elmo_b200.xmc_classifiers import Fp8XMCBCEChunkedLayer
+    layer = Fp8XMCBCEChunkedLayer(layer_cfg(wl, device, wl.batch, sched=args.sched))
+    fill_weights([p.data for p in layer.xfc_weight], wl.dim, seed=0)
+    gen = torch.Generator().manual_seed(5)
+    xs = [synth.make_embeddings(wl.batch, wl.dim, gen).to(device) for _ in range(4)]
+    k = args.topk
+    for i in range(max(3, args.warmup)):
+        layer.xfc_topk(xs[i % 4], k)
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        vals, idx = layer.xfc_topk(xs[i % 4], k)
+    e1.record()
+    torch.cuda.synchronize(device)
+    layer._handle.check()
+    ms = e0.elapsed_time(e1) / args.steps
+    flops = 2.0 * wl.batch * wl.num_labels * wl.dim
+    pk = peaks()
+    print(json.dumps({
+        "metric": "xmc_layer_topk_samples_per_sec", "value": wl.batch / (ms * 1e-3), "unit": UNIT, "n_gpus": 1,
+        "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True,
+        "dtype": "e4m3 x e4m3, fp32 accumulate, bf16 logits", "data": "synthetic",
+        "config": {"workload": f"{wl.name}: top-{k} of W[{wl.num_labels}x{wl.dim}] e4m3 for X[{wl.batch}x{wl.dim}] bf16",
+                   "l2": "weights larger than L2"},
+        "roofline": {"bound": "tensor", "kernel": "top-k", "achieved": flops / (ms * 1e-3) / 1e12,
+                     "peak": pk["bf16_sustained"] * 2.0, "unit": "TFLOP/s",
+                     "frac": flops / (ms * 1e-3) / 1e12 / (pk["bf16_sustained"] * 2.0), "traffic": None,
+                     "peak_source": pk["source"] + " bf16 sustained x2 (no measured fp8 figure)"}}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -366,6 +404,9 @@ def main():
     ap.add_argument("--rounding", default="", choices=["", "rn", "sr"], help="override the rounding mode")
     ap.add_argument("--labels", type=int, default=0, help="override the label count (small profiling captures)")
     ap.add_argument("--batch", type=int, default=0, help="override the per-rank batch")
+    ap.add_argument("--pass", dest="which", default="train", choices=["train", "topk"],
+                    help="train = the layer's train step (default); topk = the fused top-k inference pass")
+    ap.add_argument("--topk", type=int, default=5)
     args = ap.parse_args()
     rank, local_rank, world = env_int("RANK", 0), env_int("LOCAL_RANK", 0), env_int("WORLD_SIZE", 1)
     wl = synth.WORKLOADS[args.workload]
@@ -378,6 +419,11 @@ def main():
         wl = dataclasses.replace(wl, rounding=args.rounding)
     if args.impl == "reference":
         run_reference(args, wl, rank, world)
+    elif args.which == "topk":
+        if world == 1:
+            run_topk(args, wl)
+        elif rank == 0:
+            print(json.dumps({"metric": "xmc_layer_topk_samples_per_sec", "unavailable": "--pass topk is a single-GPU line"}))
     else:
         run_ours(args, wl, rank, local_rank, world)
 

@@ -232,7 +232,8 @@ struct xmc_handle {
   xmc_config cfg{};
   int sm_count = 0;
   int bpad_max = 0;
-  int sched = 0;
+  int sched = 0;                   // labels per scheduling chunk in use (set when the weights are bound)
+  int sched_cfg = 0;               // the configured / automatic value
   int64_t g_rows = 0;              // rows of G / w16 currently allocated
   std::vector<void*> w_ptrs;
   std::vector<int64_t> w_rows;
@@ -375,6 +376,7 @@ int xmc_create(const xmc_config* cfg, xmc_handle** out) {
     s = std::max(1024ll, std::min(s, 65536ll));
     h->sched = (int)(s / 128 * 128);
   }
+  h->sched_cfg = h->sched;
   const int d = cfg->dim;
   int rc = XMC_OK;
   auto A = [&](void** p, size_t bytes, bool zero) { if (rc == XMC_OK) rc = dev_alloc(h, p, bytes, zero); };
@@ -433,6 +435,12 @@ int xmc_bind_weights(xmc_handle* h, int32_t n_chunks, void* const* ptrs, const i
   h->w_rows.assign(rows, rows + n_chunks);
   h->total_rows = total;
   h->rows_per_chunk = rows[0];
+  // A weight chunk slightly longer than the automatic scheduling chunk (the reference's padding rule
+  // makes 65 552-row chunks out of 262 144 labels in 4 chunks) is taken in one piece instead of leaving a
+  // launch of a few rows behind.
+  h->sched = h->sched_cfg;
+  if (h->cfg.sched_labels <= 0 && rows[0] > h->sched && rows[0] <= h->sched + h->sched / 16)
+    h->sched = (int)round_up(rows[0], 128);
   const int64_t g_rows = std::min<int64_t>(h->sched, round_up(h->rows_per_chunk, 128));
   if (g_rows > h->g_rows) {
     const int d = h->cfg.dim;
