@@ -63,3 +63,15 @@ def sr_bits16(elem_index, seed, step):
     words = np.stack(x, axis=0)                                  # [4, ...]
     w = np.take_along_axis(words, (j >> 1)[None, ...], axis=0)[0]
     return ((w >> ((j & 1) * 16).astype(np.uint32)) & np.uint32(0xFFFF)).astype(np.uint32)
+
+
+def triton_randint(seed, offsets):
+    """``tl.randint(seed, offsets)`` of Triton (third-party dependency of the reference, pinned
+    indirectly by torch==2.6.0 -> triton 3.2.0; same definition in triton 3.6.0,
+    triton/language/random.py): Philox4x32-10 with counter = (offset, 0, 0, 0) for 32-bit offsets
+    (negative int32 offsets are bit-cast), key = (seed & 0xffffffff, seed >> 32), first output word.
+    This is the stream behind fuse_kernel.py:12,30,40 and stochastic_rounding_kernel.py:12,22.
+    Pinned by tests/golden/gpu_sr_helpers.npz (outputs of the reference's own launcher on a B200)."""
+    off = np.asarray(offsets).astype(np.int64) & 0xFFFFFFFF
+    seed = int(seed) & (2 ** 64 - 1)
+    return philox4x32_10(off.astype(np.uint64), 0, 0, 0, seed & 0xFFFFFFFF, seed >> 32)[0]

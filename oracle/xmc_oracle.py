@@ -21,17 +21,20 @@ What is restated (reference file:line, paths relative to the reference's root):
 * ``forward_logits``    -- chunked.py:48-53, chunked_fp8xmc_clf.py:45-60
 
 Parity pins: the reference ships no golden vectors or executable tests.  This oracle is
-pinned against the reference itself, imported unmodified on CPU (tests/golden/make_golden.py
-writes the fixtures; tests/test_oracle_golden.py replays them):
-  - XMCBCECHUNKEDLayer in float32 end to end (W', grad_input);
-  - XMCBCECHUNKEDLayer in bfloat16 with only the Triton ``sgd_update`` launcher replaced
-    by a round-to-nearest torch statement (Triton cannot execute without a GPU);
-  - ``torch._scaled_mm`` e4m3 forward and ``xfc_forward`` of Fp8XMCBCEChunkedLayer;
-  - ``_compute_loss``.
-The Triton kernels themselves (large_k_matmul, matmul_update, ...) cannot run in a GPU-less
-container, so for those the restatement follows the kernel source line by line and the
-expected value stated in the authors' own check (fuse_kernel.py:309-310): parity of those
-three kernels is pinned by source reading only.
+pinned against outputs of the reference itself (tests/test_oracle_golden.py and
+tests/test_oracle_golden_gpu.py replay the fixtures):
+  * imported unmodified on CPU (tests/golden/make_golden.py):
+    - XMCBCECHUNKEDLayer in float32 end to end (W', grad_input);
+    - XMCBCECHUNKEDLayer in bfloat16 with only the Triton ``sgd_update`` launcher replaced
+      by a round-to-nearest torch statement;
+    - ``torch._scaled_mm`` e4m3 forward and ``xfc_forward`` of Fp8XMCBCEChunkedLayer;
+    - ``_compute_loss``;
+  * run unmodified on a B200 (tests/golden/make_golden_gpu.py, from the staging copy that
+    oracle/make_ref.py makes): the Triton kernels ``stochastic_rounding`` / ``large_k_matmul`` /
+    ``matmul_update`` / ``kahan_matmul_update`` / ``fakefp8_matmul_update`` / ``sgd_update`` and two
+    steps each of Fp8XMCBCEChunkedLayer (real and simulated), Fp8XMCBCEChunkedHeadKahanLayer and
+    bfloat16 XMCBCECHUNKEDLayer.  With rounding mode 'sr_triton' (below) the oracle reproduces
+    the reference's stochastically rounded weights bit for bit up to accumulation-order effects.
 
 Rounding modes
   'rn'     round-to-nearest-even of the fp32 update (the value the authors compare against in
@@ -40,6 +43,10 @@ Rounding modes
            subnormals, or bf16) driven by 16 Philox bits per element (oracle/philox.py).
   'sr_ref' the reference's bit trick (fuse_kernel.py:28-36) driven by the same 16 bits widened
            to 20; kept to document that it is biased below 2^-6.
+  'sr_triton' the reference's own stochastic rounding, stream included: the bit trick driven by
+           ``tl.randint(seed, offset)`` with the per-launch seed the reference draws on the host and
+           offsets restarting at 0 in every updated tensor (fuse_kernel.py:107, chunked_fp8xmc_clf.py:113).
+           Used only to pin this file against the reference's GPU outputs.
 """
 from __future__ import annotations
 
@@ -151,6 +158,29 @@ def sr_bf16(w: np.ndarray, r16: np.ndarray) -> np.ndarray:
     return bits.view(np.float32).copy()
 
 
+def sr_triton(w: np.ndarray, seed: int, kind: str, first_offset: int = 0) -> torch.Tensor:
+    """The reference's stochastic-rounding helpers with their own random stream
+    (fuse_kernel.py:10-17,28-44; stochastic_rounding_kernel.py:10-27): element i of the flattened
+    tensor draws ``tl.randint(seed, first_offset + i)``.
+      kind 'e4m3'    + (r & 0xFFFFF), clear 20 bits, convert to e4m3 (Triton's fp32->e4m3 convert on
+                     sm_100: round-to-nearest-even, saturating to +-448 -- pinned by the fixture)
+      kind 'bf16'    + (r & 0xFFFF), clear 16 bits, convert to bf16 (exact)
+      kind 'fakefp8' + (r & 0xFFFFF), clear 20 bits, convert to bf16 (exact)
+    Returns a tensor of the target dtype with the shape of ``w``."""
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    offs = np.arange(first_offset, first_offset + w.size, dtype=np.int64).reshape(w.shape)
+    r = philox.triton_randint(seed, offs)
+    if kind == 'bf16':
+        bits = (_f32_bits(w) + (r & np.uint32(0xFFFF))) & np.uint32(0xFFFF0000)
+        return torch.from_numpy(bits.view(np.float32).copy()).to(torch.bfloat16)
+    bits = (_f32_bits(w) + (r & np.uint32(0xFFFFF))) & np.uint32(0xFFF00000)
+    t = torch.from_numpy(bits.view(np.float32).copy())
+    if kind == 'fakefp8':
+        return t.to(torch.bfloat16)
+    assert kind == 'e4m3'
+    return cast_e4m3_sat(t)
+
+
 _CLIB = False
 
 
@@ -186,6 +216,9 @@ def round_update(w32: torch.Tensor, w_dtype: torch.dtype, rounding: str,
         if w_dtype == E4M3:
             return cast_e4m3_sat(w32)
         return w32.to(w_dtype)
+    if rounding == 'sr_triton':     # here ``seed`` is the launch's host-drawn seed, ``first_elem`` the in-tensor offset
+        wn = w32.detach().to(torch.float32).contiguous().numpy()
+        return sr_triton(wn, seed, 'e4m3' if w_dtype == E4M3 else 'bf16', first_elem)
     n = w32.numel()
     clib = _c_lib()
     if clib is not None and rounding == 'sr' and w_dtype in (E4M3, torch.bfloat16):
@@ -254,6 +287,7 @@ def fp8_chunked_step(w_chunks: Sequence[torch.Tensor], x: torch.Tensor, labels: 
                      seed: int = 0, step: int = 0, w_scale: float = 1.0,
                      label_offset: int = 0, compute_loss: bool = False,
                      kahan: Optional[torch.Tensor] = None,
+                     chunk_seeds: Optional[Sequence[int]] = None,
                      ) -> Tuple[List[torch.Tensor], torch.Tensor, float]:
     """One ``Fp8XMCBCEChunkedLayer.xfc_forward_backward`` (chunked_fp8xmc_clf.py:81-123).
 
@@ -263,6 +297,8 @@ def fp8_chunked_step(w_chunks: Sequence[torch.Tensor], x: torch.Tensor, labels: 
                    Philox element index, so sharded and unsharded runs draw the same bits.
     kahan    : optional compensation buffer for rows [0, num_head) of chunk 0
                (chunked_head_kahan_fp8xmc_clf.py:127-131), bf16 or e5m2; updated in place.
+    chunk_seeds : rounding 'sr_triton' only -- the seed the reference draws on the host for each
+               chunk (chunked_fp8xmc_clf.py:113); offsets restart at 0 in every updated tensor.
     Returns (new chunks, grad_X fp32 [B, d] (not yet cast to bf16), loss).
     """
     assert x.dtype == torch.bfloat16
@@ -295,19 +331,30 @@ def fp8_chunked_step(w_chunks: Sequence[torch.Tensor], x: torch.Tensor, labels: 
         grad_x += gx * s32 if s32 != 1.0 else gx
         acc = matmul_acc(g, x32)                               # fuse_kernel.py:84-96 (bf16 embed)
         first = lo * d
+        sd = seed
+        tri = rounding == 'sr_triton'
+        if tri:
+            sd, first = int(chunk_seeds[len(new_chunks)]), 0
         if kahan is not None and row0 == 0:
             nh = kahan.shape[0]
             k32 = kahan.to(torch.float32)
             wk = fused_update(w32[:nh] + k32, acc[:nh], lr_eff)            # fuse_kernel.py:257-258
-            head = round_update(wk, E4M3, rounding, seed, step, first)
+            head = round_update(wk, E4M3, rounding, sd, step, first)
             knew = k32 + w32[:nh] - head.to(torch.float32) - lr_eff * acc[:nh]   # :267
             kahan.copy_(knew.to(kahan.dtype))
+            # the tail is a launch of its own with the same seed: its offsets restart at 0
+            # (chunked_head_kahan_fp8xmc_clf.py:131)
             tail = round_update(fused_update(w32[nh:], acc[nh:], lr_eff), E4M3, rounding,
-                                seed, step, first + nh * d)
+                                sd, step, 0 if tri else first + nh * d)
             new = torch.cat([head, tail], 0)
+        elif simulated and tri:
+            # fuse_kernel.py:134-182 on the bf16 copy, then chunked_fp8xmc_clf.py:116 casts it back
+            w_upd = fused_update(w32, acc, lr_eff)
+            w16 = sr_triton(w_upd.numpy(), sd, 'fakefp8', 0)
+            new = w16.to(E4M3)
         else:
             w_upd = fused_update(w32, acc, lr_eff)             # fuse_kernel.py:105
-            new = round_update(w_upd, E4M3, rounding, seed, step, first)
+            new = round_update(w_upd, E4M3, rounding, sd, step, first)
         new_chunks.append(new)
         row0 += li
     return new_chunks, grad_x, loss
@@ -316,6 +363,7 @@ def fp8_chunked_step(w_chunks: Sequence[torch.Tensor], x: torch.Tensor, labels: 
 def chunked_step(w: torch.Tensor, x: torch.Tensor, labels: torch.Tensor, lr: float, *,
                  num_chunks: int, wd: float = 0.0, rounding: str = 'rn', seed: int = 0,
                  step: int = 0, label_offset: int = 0, compute_loss: bool = False,
+                 chunk_seeds: Optional[Sequence[int]] = None,
                  ) -> Tuple[torch.Tensor, torch.Tensor, float]:
     """One ``XMCBCECHUNKEDLayer.xfc_forward_backward`` (chunked.py:75-133).
 
@@ -350,7 +398,10 @@ def chunked_step(w: torch.Tensor, x: torch.Tensor, labels: torch.Tensor, lr: flo
         else:
             lr32 = float(np.float32(lr))
             upd = (wc.to(torch.float64) - dw.to(torch.float64) * lr32).to(torch.float32)
-            w_new[s:e] = round_update(upd, dt, rounding, seed, step, (label_offset + s) * d)
+            if rounding == 'sr_triton':                        # chunked.py:126-127: one host seed per chunk
+                w_new[s:e] = round_update(upd, dt, rounding, int(chunk_seeds[c]), step, 0)
+            else:
+                w_new[s:e] = round_update(upd, dt, rounding, seed, step, (label_offset + s) * d)
     return w_new, grad_x, loss
 
 
