@@ -9,12 +9,9 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT_DIR = os.path.join(HERE, "_build")
-# tuning aid: XMC_NVCC_DEFS="-DA=1 -DB=2" builds a variant into its own file
-_DEFS = os.environ.get("XMC_NVCC_DEFS", "").split()
-_TAG = ("_" + "_".join(d.lstrip("-D").replace("=", "") for d in _DEFS)) if _DEFS else ""
-LIB = os.path.join(OUT_DIR, f"libelmo_xmc{_TAG}.so")
+LIB = os.path.join(OUT_DIR, "libelmo_xmc.so")
 SOURCES = ["xmc_lib.cu"]
-HEADERS = ["ptx.cuh", "numerics.cuh", "gemm_engine.cuh", "gemm_engine2.cuh", "xmc_policies.cuh", "aux_kernels.cuh", "gradx_kernel.cuh",
+HEADERS = ["ptx.cuh", "numerics.cuh", "gemm_engine.cuh", "xmc_policies.cuh", "aux_kernels.cuh", "gradx_kernel.cuh",
            os.path.join("..", "..", "include", "elmo_xmc.h")]
 
 
@@ -35,7 +32,7 @@ def build(force=False, verbose=False):
     cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
            "-Xcompiler", "-fPIC", "-shared", "-cudart", "static",
            "-Xptxas", "-v" if verbose else "-warn-spills",
-           "-o", LIB] + _DEFS + [os.path.join(CSRC, s) for s in SOURCES]
+           "-o", LIB] + [os.path.join(CSRC, s) for s in SOURCES]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)

@@ -209,6 +209,12 @@ __global__ void e4m3_to_bf16_kernel(const uint4* __restrict__ src, uint4* __rest
   }
 }
 
+// out[i] = bf16(sigmoid(in[i])) exactly as the forward epilogue computes it (test hook)
+__global__ void sigmoid_probe_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = __float2bfloat16_rn(fast_sigmoid(__bfloat162float(in[i])));
+}
+
 // grad_X[b][c] = scale * sum_s partial[s][b][c], s ascending (fixed order)
 __global__ void reduce_gradx_kernel(const float* __restrict__ partial, int n_splits, int batch, int bpad,
                                     int d, float scale, float* __restrict__ out32,

@@ -9,14 +9,18 @@
 // TMEM allocation from ever blocking).  The accumulator is double buffered (2 x 256 columns) so the
 // epilogue of tile t overlaps the main loop of tile t+1.  Every wait is bounded (ptx.cuh).
 //
-// A policy supplies: operand kind/majorness, the tile -> job mapping and the epilogue.
+// A policy supplies: operand kind/majorness, the tile -> job mapping and the epilogue.  A policy with
+// kCTile set also has the producer fetch, per tile, the 128 x 256-byte block of a third tensor (the
+// weights the update epilogue reads and rewrites) into a two-deep shared-memory ring while the tile's
+// main loop runs; the epilogue rewrites the block in place and one TMA store writes it back, so no
+// epilogue thread ever touches global memory.
 #pragma once
 #include "ptx.cuh"
 
 namespace xmc {
 
 constexpr int kMaxEpiWarps = 16;            // a policy picks 4, 8 or 16 epilogue warps (kEpiWarps)
-constexpr int kStages = 4;
+constexpr int kMaxStages = 4;               // a policy picks its ring depth (kStages <= kMaxStages)
 constexpr int kTileM = 128;                 // UMMA M = TMEM lanes
 constexpr int kTileN = 256;                 // UMMA N upper bound = TMEM columns per accumulator
 constexpr int kRowBytes = 128;              // swizzle span: one operand row per k-step
@@ -25,6 +29,8 @@ constexpr int kStageBBytes = kTileN * kRowBytes;   // 32 KB
 constexpr int kStageBytes = kStageABytes + kStageBBytes;
 constexpr int kTmemCols = 512;
 constexpr int kMnBoxBytes = 64 * kRowBytes;  // MN-major operands arrive as boxes of 64 k-rows x 128 B
+constexpr int kCHalfBytes = kTileM * 128;    // epilogue-input tile: two 128-byte-swizzled halves of 128 rows x 128 B
+constexpr int kCTileBytes = 2 * kCHalfBytes; // 32 KB
 
 struct Job {
   int a0;        // K-major: first row of A;   MN-major: first M index
@@ -41,29 +47,51 @@ struct EpiCtx {
   int h;        // this warp handles 32-column groups h, h+nsplit, h+2*nsplit, ...
   int nsplit;
   int slot;     // epilogue warp index 0..kEpiWarps-1
+  uint8_t* ctile;         // this tile's read-modify-write block in shared memory (kCTile policies)
+  uint32_t* bitmap;       // kBitmap policies: kTileM x kTileN bits, the positives of one (label tile, batch tile)
 };
 
 struct SharedTail {
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
+  uint64_t c_full[2];      // epilogue tile landed (kCTile policies)
+  uint64_t c_done[2];      // all epilogue warps have rewritten their part of it
+  uint64_t c_empty[2];     // it has been stored back and may be refilled
   uint32_t tmem_base;
   Ctl ctl;
-  uint32_t bitmap[kTileM * (kTileN / 32)];   // positives of one (label tile, batch tile)
 };
+constexpr int kBitmapBytes = kTileM * (kTileN / 32) * 4;
 
-constexpr int kSmemBytes = kStages * kStageBytes + (int)sizeof(SharedTail) + 1024;
-static_assert(kSmemBytes <= 232448, "exceeds the 227 KB of shared memory a CTA can get");
+
+template <class Policy>
+__host__ __device__ constexpr int smem_bytes() {
+  return Policy::kStages * kStageBytes + (Policy::kCTile ? Policy::kCBufs * kCTileBytes : 0) +
+         (Policy::kBitmap ? kBitmapBytes : 0) + (int)sizeof(SharedTail) + 1024;
+}
+
+// Address of the 8 bytes at byte column `col` (multiple of 8) of row `row` of an epilogue tile, as the
+// 128-byte-swizzling TMA copies lay it out (two halves of 128 rows x 128 B; 16-byte pieces XOR row & 7).
+__device__ __forceinline__ uint2* ctile_ptr8(uint8_t* tile, int row, int col) {
+  uint8_t* rowp = tile + (col >> 7) * kCHalfBytes + row * 128;
+  return reinterpret_cast<uint2*>(rowp + (((((col & 127) >> 4) ^ (row & 7)) << 4) | (col & 8)));
+}
 
 template <class Policy>
 __global__ void __launch_bounds__(64 + 32 * Policy::kEpiWarps, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-            const typename Policy::Params p) {
+            const __grid_constant__ CUtensorMap map_c, const typename Policy::Params p) {
+  constexpr int kStages = Policy::kStages;
+  static_assert(kStages >= 2 && kStages <= kMaxStages, "ring depth");
+  static_assert(smem_bytes<Policy>() <= 232448, "exceeds the 227 KB of shared memory a CTA can get");
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the 128-byte swizzle pattern is a function of address bits [4,10)
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  SharedTail& sh = *reinterpret_cast<SharedTail*>(smem + kStages * kStageBytes);
+  uint8_t* smem_c = smem + kStages * kStageBytes;
+  uint8_t* smem_bm = smem_c + (Policy::kCTile ? Policy::kCBufs * kCTileBytes : 0);
+  SharedTail& sh = *reinterpret_cast<SharedTail*>(smem_bm + (Policy::kBitmap ? kBitmapBytes : 0));
+  constexpr uint32_t kCBufs = Policy::kCTile ? (uint32_t)Policy::kCBufs : 1u;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int n_tiles = Policy::num_tiles(p);
@@ -76,11 +104,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&sh.tmem_full[b]), 1);
       mbar_init(smem_u32(&sh.tmem_empty[b]), 32 * Policy::kEpiWarps);
+      mbar_init(smem_u32(&sh.c_full[b]), 1);
+      mbar_init(smem_u32(&sh.c_done[b]), Policy::kEpiWarps);
+      mbar_init(smem_u32(&sh.c_empty[b]), 1);
     }
     sh.ctl.abort = 0;
     fence_barrier_init();
     tma_prefetch_desc(&map_a);
     tma_prefetch_desc(&map_b);
+    if constexpr (Policy::kCTile) tma_prefetch_desc(&map_c);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(&sh.tmem_base), kTmemCols);
@@ -95,85 +127,127 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
-      uint32_t it = 0;
+    {
+      // Both issuing roles share their scheduler with busy epilogue warps, so every instruction here
+      // waits its turn.  The whole warp runs the loop on warp-uniform values (uniform registers and
+      // datapath: no per-operand moves from the vector registers) and one elected lane issues; stage
+      // index and phase are running counters, addresses and descriptors advance by adds.
+      uint32_t s = 0, ph = 0, t_local = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+      const uint32_t full0 = smem_u32(&sh.full[0]), empty0 = smem_u32(&sh.empty[0]), stage0 = smem_u32(smem);
+      for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++t_local) {
         Job job;
         Policy::job(p, tile, job);
-        for (int k = 0; k < job.k_steps; ++k, ++it) {
-          const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
-          if (!mbar_wait(smem_u32(&sh.empty[s]), ph ^ 1u, &sh.ctl, p.status, 100 + (int)s)) {
+        // The epilogue's read-modify-write block of this tile is requested as soon as its slot has been
+        // stored back (the epilogue of tile t - kCBufs); until then the operand loads go ahead, and the
+        // slot is polled once per k-step without blocking.
+        bool c_pending = Policy::kCTile;
+        const uint32_t cb = t_local % kCBufs, cph = (t_local / kCBufs) & 1u;
+        auto issue_c = [&]() {
+          if constexpr (Policy::kCTile) {
+            const uint32_t bar = smem_u32(&sh.c_full[cb]);
+            const uint32_t dst = smem_u32(smem_c + cb * kCTileBytes);
+            if (elect_one()) {
+              mbar_arrive_expect_tx(bar, kCTileBytes);
+              tma_load_2d(dst, &map_c, bar, Policy::c_col(job), Policy::c_row(job));
+              tma_load_2d(dst + kCHalfBytes, &map_c, bar, Policy::c_col(job) + 128, Policy::c_row(job));
+            }
+            __syncwarp();
+          }
+          c_pending = false;
+        };
+        int kk = job.k_begin * (Policy::kMnMajor ? 64 : Policy::kElemsPerRow);
+        for (int k = 0; k < job.k_steps; ++k) {
+          if constexpr (Policy::kCTile) {
+            if (c_pending && __any_sync(0xffffffffu, mbar_try_wait(smem_u32(&sh.c_empty[cb]), cph ^ 1u))) issue_c();
+          }
+          if (!mbar_wait_warp(empty0 + 8u * s, ph ^ 1u, &sh.ctl, p.status, 100 + (int)s)) {
             ok = false;
             break;
           }
-          const uint32_t bar = smem_u32(&sh.full[s]);
-          const uint32_t sa = smem_u32(smem + s * kStageBytes);
+          const uint32_t bar = full0 + 8u * s;
+          const uint32_t sa = stage0 + s * kStageBytes;
           const uint32_t sb = sa + kStageABytes;
-          const int kk = job.k_begin + k;
           if constexpr (!Policy::kMnMajor) {
-            mbar_arrive_expect_tx(bar, kStageBytes);
-            tma_load_2d(sa, &map_a, bar, kk * Policy::kElemsPerRow, job.a0);
-            tma_load_2d(sb, &map_b, bar, kk * Policy::kElemsPerRow, job.b0);
+            if (elect_one()) {
+              mbar_arrive_expect_tx(bar, kStageBytes);
+              tma_load_2d(sa, &map_a, bar, kk, job.a0);
+              tma_load_2d(sb, &map_b, bar, kk, job.b0);
+            }
+            kk += Policy::kElemsPerRow;
           } else {
             const int nb = (job.n_eff + 63) >> 6;
-            mbar_arrive_expect_tx(bar, (2 + nb) * kMnBoxBytes);
-            for (int j = 0; j < 2; ++j)
-              tma_load_2d(sa + j * kMnBoxBytes, &map_a, bar, job.a0 + 64 * j, kk * 64);
-            for (int j = 0; j < nb; ++j)
-              tma_load_2d(sb + j * kMnBoxBytes, &map_b, bar, job.b0 + 64 * j, kk * 64);
+            if (elect_one()) {
+              mbar_arrive_expect_tx(bar, (2 + nb) * kMnBoxBytes);
+              for (int j = 0; j < 2; ++j)
+                tma_load_2d(sa + j * kMnBoxBytes, &map_a, bar, job.a0 + 64 * j, kk);
+              for (int j = 0; j < nb; ++j)
+                tma_load_2d(sb + j * kMnBoxBytes, &map_b, bar, job.b0 + 64 * j, kk);
+            }
+            kk += 64;
+          }
+          __syncwarp();
+          if (++s == (uint32_t)kStages) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+        if constexpr (Policy::kCTile) {
+          if (ok && c_pending) {
+            if (!mbar_wait_warp(smem_u32(&sh.c_empty[cb]), cph ^ 1u, &sh.ctl, p.status, 600 + (int)cb)) break;
+            issue_c();
           }
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
-      uint32_t it = 0, t_local = 0;
+    {
+      uint32_t s = 0, ph = 0, t_local = 0;
       bool ok = true;
+      const uint32_t full0 = smem_u32(&sh.full[0]), empty0 = smem_u32(&sh.empty[0]);
+      // K-major, 128B swizzle: rows of 128 B, 8-row groups 1024 B apart; one UMMA eats 32 B of K.
+      // MN-major, 128B swizzle: blocks of 64 MN-elements (128 B) x 64 k-rows; 8-k-row groups 1024 B apart
+      // (stride offset), MN blocks 8192 B apart (leading offset); one UMMA eats 16 k-rows = 2048 B.
+      constexpr uint32_t kLbo = Policy::kMnMajor ? (uint32_t)kMnBoxBytes : 16u;
+      constexpr uint32_t kDescStep = Policy::kMnMajor ? 128u : 2u;      // descriptor address units (16 B) per UMMA
+      constexpr uint32_t desc_hi = smem_desc_hi_sw128(1024);
+      const uint32_t a_lo0 = smem_desc_lo(smem_u32(smem), kLbo);
       for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++t_local) {
         Job job;
         Policy::job(p, tile, job);
         const uint32_t buf = t_local & 1u, aph = (t_local >> 1) & 1u;
-        if (!mbar_wait(smem_u32(&sh.tmem_empty[buf]), aph ^ 1u, &sh.ctl, p.status, 200 + (int)buf)) break;
+        if (!mbar_wait_warp(smem_u32(&sh.tmem_empty[buf]), aph ^ 1u, &sh.ctl, p.status, 200 + (int)buf)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * kTileN;
         const uint32_t idesc = make_idesc(kTileM, (uint32_t)job.n_eff, Policy::kFmt, Policy::kFmt,
                                           Policy::kMnMajor ? 1u : 0u, Policy::kMnMajor ? 1u : 0u);
-        for (int k = 0; k < job.k_steps; ++k, ++it) {
-          const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
-          if (!mbar_wait(smem_u32(&sh.full[s]), ph, &sh.ctl, p.status, 300 + (int)s)) {
+        uint32_t acc = 0u;
+        for (int k = 0; k < job.k_steps; ++k) {
+          if (!mbar_wait_warp(full0 + 8u * s, ph, &sh.ctl, p.status, 300 + (int)s)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + s * kStageBytes);
-          const uint32_t sb = sa + kStageABytes;
-          if constexpr (!Policy::kMnMajor) {
-            // K-major, 128B swizzle: rows of 128 B, 8-row groups 1024 B apart; one UMMA eats 32 B of K
-            const uint64_t da = smem_desc_sw128(sa, 16, 1024);
-            const uint64_t db = smem_desc_sw128(sb, 16, 1024);
+          const uint32_t a_lo = a_lo0 + s * (uint32_t)(kStageBytes >> 4);
+          const uint32_t b_lo = a_lo + (uint32_t)(kStageABytes >> 4);
+          if (elect_one()) {
 #pragma unroll
-            for (int u = 0; u < kRowBytes / 32; ++u) {
-              const uint32_t acc = (k | u) != 0 ? 1u : 0u;
-              if constexpr (Policy::kFp8) umma_f8(d_tmem, da + 2u * u, db + 2u * u, idesc, acc);
-              else umma_f16(d_tmem, da + 2u * u, db + 2u * u, idesc, acc);
+            for (uint32_t u = 0; u < 4; ++u) {
+              if constexpr (Policy::kFp8) umma_f8_lohi(d_tmem, a_lo + kDescStep * u, b_lo + kDescStep * u, desc_hi, idesc, u == 0 ? acc : 1u);
+              else umma_f16_lohi(d_tmem, a_lo + kDescStep * u, b_lo + kDescStep * u, desc_hi, idesc, u == 0 ? acc : 1u);
             }
-          } else {
-            // MN-major, 128B swizzle: blocks of 64 MN-elements (128 B) x 64 k-rows; 8-k-row groups
-            // 1024 B apart (stride offset), MN blocks 8192 B apart (leading offset); one UMMA eats
-            // 16 k-rows = 2048 B
-            const uint64_t da = smem_desc_sw128(sa, kMnBoxBytes, 1024);
-            const uint64_t db = smem_desc_sw128(sb, kMnBoxBytes, 1024);
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const uint32_t acc = (k | u) != 0 ? 1u : 0u;
-              umma_f16(d_tmem, da + 128u * u, db + 128u * u, idesc, acc);
-            }
+            umma_commit(empty0 + 8u * s);          // slot is free once these MMAs have read it
           }
-          umma_commit(smem_u32(&sh.empty[s]));     // slot is free once these MMAs have read it
+          __syncwarp();
+          acc = 1u;
+          if (++s == (uint32_t)kStages) {
+            s = 0;
+            ph ^= 1u;
+          }
         }
-        if (ok) umma_commit(smem_u32(&sh.tmem_full[buf]));
+        if (ok && elect_one()) umma_commit(smem_u32(&sh.tmem_full[buf]));
+        __syncwarp();
       }
     }
   } else {
@@ -186,6 +260,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     ec.h = (warp - 2) >> 2;                         // which of the column-group phases this warp takes
     ec.nsplit = Policy::kEpiWarps / 4;
     ec.slot = warp - 2;
+    ec.ctile = nullptr;
+    ec.bitmap = Policy::kBitmap ? reinterpret_cast<uint32_t*>(smem_bm) : nullptr;
     const int q = ec.q;
     typename Policy::EpilogueState st;
     Policy::epilogue_begin(p, st);
@@ -196,11 +272,39 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       const uint32_t buf = t_local & 1u, aph = (t_local >> 1) & 1u;
       Policy::epilogue_pre(p, job, sh, ec, st);          // overlaps the tile's main loop
       if (!mbar_wait_relaxed(smem_u32(&sh.tmem_full[buf]), aph, &sh.ctl, p.status, 400 + (int)buf)) break;
+      const uint32_t cb = t_local % kCBufs, cph = (t_local / kCBufs) & 1u;
+      if constexpr (Policy::kCTile) {
+        if (!mbar_wait(smem_u32(&sh.c_full[cb]), cph, &sh.ctl, p.status, 610 + (int)cb)) break;
+        ec.ctile = smem_c + cb * kCTileBytes;
+      }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * kTileN;
       Policy::epilogue(p, job, taddr, job.k_steps > 0, sh, ec, st);
       tc_fence_before();
       mbar_arrive(smem_u32(&sh.tmem_empty[buf]));
+      if constexpr (Policy::kCTile) {
+        // The epilogue rewrote its part of the block in place.  Once every warp has done so, one thread
+        // stores the block back with TMA (whole lines; rows and columns outside the tensor are clipped)
+        // and, when the store has read shared memory, hands the slot back to the producer.
+        fence_proxy_async();                             // generic-proxy writes -> async-proxy (TMA) reads
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sh.c_done[cb]));
+        if (ec.slot == 0 && lane == 0) {
+          if (mbar_wait(smem_u32(&sh.c_done[cb]), cph, &sh.ctl, p.status, 620 + (int)cb)) {
+            const uint32_t src = smem_u32(smem_c + cb * kCTileBytes);
+            tma_store_2d(&map_c, src, Policy::c_col(job), Policy::c_row(job));
+            tma_store_2d(&map_c, src + kCHalfBytes, Policy::c_col(job) + 128, Policy::c_row(job));
+            bulk_commit_group();
+            bulk_wait_read_all();
+            mbar_arrive(smem_u32(&sh.c_empty[cb]));
+          }
+        }
+        __syncwarp();                                    // the warp-wide TMEM loads of the next tile need all lanes
+      }
+    }
+    if constexpr (Policy::kCTile) {
+      if (ec.slot == 0 && lane == 0) bulk_wait_all();    // the stores have landed before the CTA retires
+      __syncwarp();
     }
     Policy::epilogue_end(p, sh, ec, st);
   }

@@ -115,56 +115,73 @@ gradx_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant__ 
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
-      for (int i = 0; i < k_steps; ++i) {
-        const int krow = (k_begin + i) * kGxRows;
-        const uint32_t s = i % kGxStages, ph = (i / kGxStages) & 1u;
+    // The whole warp runs the loop on warp-uniform values (uniform registers: the TMA instructions take
+    // their operands there) and one elected lane issues; ring indices are running counters.
+    {
+      uint32_t s = 0, ph = 0, rs = 0, rph = 0;
+      int krow = k_begin * kGxRows;
+      for (int i = 0; i < k_steps; ++i, krow += kGxRows) {
         if constexpr (CONVERT) {
-          const uint32_t rs = i % kGxRawStages, rph = (i / kGxRawStages) & 1u;
-          if (!mbar_wait(smem_u32(&sh.raw_empty[rs]), rph ^ 1u, &sh.ctl, p.status, 500 + (int)rs)) break;
-          const uint32_t rb = smem_u32(&sh.raw_full[rs]);
-          mbar_arrive_expect_tx(rb, kGxRawBytes);
-          // one box: [4 feature blocks][32 rows][64 B]
-          tma_load_3d(smem_u32(smem_r + rs * kGxRawBytes), &map_w, rb, 0, krow, c0 >> 6);
+          if (!mbar_wait_warp(smem_u32(&sh.raw_empty[rs]), rph ^ 1u, &sh.ctl, p.status, 500 + (int)rs)) break;
+          if (elect_one()) {
+            const uint32_t rb = smem_u32(&sh.raw_full[rs]);
+            mbar_arrive_expect_tx(rb, kGxRawBytes);
+            // one box: [4 feature blocks][32 rows][64 B]
+            tma_load_3d(smem_u32(smem_r + rs * kGxRawBytes), &map_w, rb, 0, krow, c0 >> 6);
+          }
+          __syncwarp();
+          if (++rs == (uint32_t)kGxRawStages) { rs = 0; rph ^= 1u; }
         }
-        if (!mbar_wait(smem_u32(&sh.mma_done[s]), ph ^ 1u, &sh.ctl, p.status, 510 + (int)s)) break;
-        const uint32_t ab = smem_u32(&sh.a_full[s]);
-        mbar_arrive_expect_tx(ab, kGxABytes);
-        // one box: [4 batch blocks][32 rows][128 B], blocks beyond the batch are zero-filled
-        tma_load_3d(smem_u32(smem_a + s * kGxABytes), &map_g, ab, 0, krow, b0 >> 6);
-        if constexpr (!CONVERT) {
-          const uint32_t bb = smem_u32(&sh.b_full[s]);
-          mbar_arrive_expect_tx(bb, kGxBBytes);
-          tma_load_3d(smem_u32(smem_b + s * kGxBBytes), &map_w, bb, 0, krow, c0 >> 6);
+        if (!mbar_wait_warp(smem_u32(&sh.mma_done[s]), ph ^ 1u, &sh.ctl, p.status, 510 + (int)s)) break;
+        if (elect_one()) {
+          const uint32_t ab = smem_u32(&sh.a_full[s]);
+          mbar_arrive_expect_tx(ab, kGxABytes);
+          // one box: [4 batch blocks][32 rows][128 B], blocks beyond the batch are zero-filled
+          tma_load_3d(smem_u32(smem_a + s * kGxABytes), &map_g, ab, 0, krow, b0 >> 6);
+          if constexpr (!CONVERT) {
+            const uint32_t bb = smem_u32(&sh.b_full[s]);
+            mbar_arrive_expect_tx(bb, kGxBBytes);
+            tma_load_3d(smem_u32(smem_b + s * kGxBBytes), &map_w, bb, 0, krow, c0 >> 6);
+          }
         }
+        __syncwarp();
+        if (++s == (uint32_t)kGxStages) { s = 0; ph ^= 1u; }
       }
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
+    {
       const uint32_t idesc = make_idesc(128, (uint32_t)n_eff, 1u, 1u, 1u, 1u);
+      // MN-major, 128B swizzle: 64-element blocks kGxBlockBytes apart (leading offset), 8-row
+      // groups 1024 B apart (stride offset); one UMMA consumes 16 label rows = 2048 B per block
+      constexpr uint32_t desc_hi = smem_desc_hi_sw128(1024);
+      const uint32_t a_lo0 = smem_desc_lo(smem_u32(smem_a), kGxBlockBytes);
+      const uint32_t b_lo0 = smem_desc_lo(smem_u32(smem_b), kGxBlockBytes);
       bool ok = true;
+      uint32_t s = 0, ph = 0, acc = 0u;
       for (int i = 0; i < k_steps; ++i) {
-        const uint32_t s = i % kGxStages, ph = (i / kGxStages) & 1u;
-        if (!mbar_wait(smem_u32(&sh.a_full[s]), ph, &sh.ctl, p.status, 520 + (int)s) ||
-            !mbar_wait(smem_u32(&sh.b_full[s]), ph, &sh.ctl, p.status, 530 + (int)s)) {
+        if (!mbar_wait_warp(smem_u32(&sh.a_full[s]), ph, &sh.ctl, p.status, 520 + (int)s) ||
+            !mbar_wait_warp(smem_u32(&sh.b_full[s]), ph, &sh.ctl, p.status, 530 + (int)s)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        const uint32_t sa = smem_u32(smem_a + s * kGxABytes), sb = smem_u32(smem_b + s * kGxBBytes);
-        // MN-major, 128B swizzle: 64-element blocks kGxBlockBytes apart (leading offset), 8-row
-        // groups 1024 B apart (stride offset); one UMMA consumes 16 label rows = 2048 B per block
-        const uint64_t db = smem_desc_sw128(sb, kGxBlockBytes, 1024);
-        for (int hm = 0; hm < m_halves; ++hm) {
-          const uint64_t da = smem_desc_sw128(sa + hm * 2 * kGxBlockBytes, kGxBlockBytes, 1024);
+        if (elect_one()) {
+          const uint32_t a_lo = a_lo0 + s * (uint32_t)(kGxABytes >> 4), b_lo = b_lo0 + s * (uint32_t)(kGxBBytes >> 4);
+          for (int hm = 0; hm < m_halves; ++hm) {
 #pragma unroll
-          for (int u = 0; u < kGxRows / 16; ++u)
-            umma_f16(tmem_base + hm * 256, da + 128u * u, db + 128u * u, idesc, (i | u) != 0 ? 1u : 0u);
+            for (uint32_t u = 0; u < kGxRows / 16; ++u)
+              umma_f16_lohi(tmem_base + hm * 256, a_lo + (uint32_t)hm * (2u * kGxBlockBytes >> 4) + 128u * u, b_lo + 128u * u,
+                            desc_hi, idesc, u == 0 ? acc : 1u);
+          }
+          umma_commit(smem_u32(&sh.mma_done[s]));
         }
-        umma_commit(smem_u32(&sh.mma_done[s]));
+        __syncwarp();
+        acc = 1u;
+        if (++s == (uint32_t)kGxStages) { s = 0; ph ^= 1u; }
       }
-      if (ok) umma_commit(smem_u32(&sh.tmem_full));
+      if (ok && elect_one()) umma_commit(smem_u32(&sh.tmem_full));
+      __syncwarp();
     }
   } else {
     // -------------------- converters, then epilogue (warps 2..9) --------------------

@@ -27,8 +27,8 @@ __device__ __forceinline__ uint16_t float2_to_e4m3x2(float x, float y) {
   return (uint16_t)__nv_cvt_float2_to_fp8x2(make_float2(x, y), __NV_SATFINITE, __NV_E4M3);
 }
 
-// 1 / (1 + 2^(-z log2 e)) with the two approximate special-function ops (relative error ~2^-22,
-// far below the bf16 rounding that follows)
+// sigmoid(z) = 1 / (1 + 2^(-z log2 e)) with the two approximate special-function ops (relative error
+// ~2^-22, far below the bf16 rounding that follows).
 __device__ __forceinline__ float fast_sigmoid(float z) {
   float e, r;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(z * -1.4426950408889634f));
@@ -59,20 +59,24 @@ __device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint2 k) {
 }
 
 // Exact stochastic rounding of fp32 w onto the e4m3 grid (subnormals included) with 16 random
-// bits; returns a float that lies on the grid.  |w| is clamped to 448, NaN propagates.
-// Normal range: add r16<<4 into the 20 discarded mantissa bits and truncate (the reference's bit
-// trick, fuse_kernel.py:28-36).  Below 2^-6 the grid is uniform (step 2^-9): shift the value into
-// the binade [2^-6, 2^-5), whose 3-bit step is 2^-9, round there and shift back (both exact).
+// bits; returns a float that lies on the grid (or beyond +-448: the saturating e4m3 conversion
+// that follows clamps it).  The sign is kept, also for a zero result; NaN propagates.
+//
+// The reference's bit trick (fuse_kernel.py:28-36) adds the random bits into the 20 mantissa bits
+// an e4m3 normal discards and truncates; below 2^-6 the e4m3 grid is uniform (step 2^-9) and the
+// trick no longer sees it.  Scaling by 2^-120 first maps e4m3's smallest normal onto fp32's
+// (2^-126): e4m3 subnormals become fp32 subnormals, whose bit pattern is fixed point with bit 20
+// worth exactly one e4m3 step, so ONE add-and-mask is exact stochastic rounding on the whole grid,
+// carries from the subnormal into the normal range included.  Both scalings are exact (the first
+// rounds only below 2^-149, i.e. 2^-29 before scaling).  Needs fp32 denormals (no -ftz).
+constexpr float kSrDown = 7.52316384526264005e-37f;   // 2^-120
+constexpr float kSrUp = 1.32922799578491587e+36f;     // 2^120
+__device__ __forceinline__ float sr_e4m3_finite(float w, uint32_t r16) {
+  const uint32_t b = (__float_as_uint(w * kSrDown) + (r16 << 4)) & 0xFFF00000u;
+  return __uint_as_float(b) * kSrUp;
+}
 __device__ __forceinline__ float sr_e4m3(float w, uint32_t r16) {
-  // Branch-free and light on the integer/compare pipe: this runs for every weight element.  The bit
-  // trick works on the signed value directly (adding to a sign-magnitude pattern grows the
-  // magnitude); the shift into the binade [2^-6, 2^-5) uses an offset carrying the sign of w.
-  // Values beyond +-448 and infinities are left to the saturating e4m3 conversion that follows; a
-  // result of zero is +0.
-  const uint32_t wb = __float_as_uint(w);
-  const float offs = __uint_as_float((fabsf(w) < 0.015625f ? 0x3C800000u : 0u) | (wb & 0x80000000u));
-  const uint32_t bits = (__float_as_uint(w + offs) + (r16 << 4)) & 0xFFF00000u;
-  const float y = __uint_as_float(bits) - offs;
+  const float y = sr_e4m3_finite(w, r16);               // +-Inf stays +-Inf; a NaN pattern may wrap
   return w != w ? w : y;
 }
 // Stochastic rounding onto the bf16 grid: add 16 random bits below the kept mantissa, truncate

@@ -14,7 +14,6 @@
 #include "../../include/elmo_xmc.h"
 #include "aux_kernels.cuh"
 #include "gemm_engine.cuh"
-#include "gemm_engine2.cuh"
 #include "gradx_kernel.cuh"
 #include "xmc_policies.cuh"
 
@@ -194,32 +193,21 @@ int gradx_configure() {
 
 template <class Policy>
 int launch_gemm(const CUtensorMap& a, const CUtensorMap& b, const typename Policy::Params& p, int n_tiles,
-                int sm_count, cudaStream_t stream, int grid_override = 0) {
+                int sm_count, cudaStream_t stream, int grid_override = 0, const CUtensorMap* c = nullptr) {
   if (n_tiles <= 0) return XMC_OK;
   auto kern = xmc::gemm_kernel<Policy>;
+  constexpr int smem = xmc::smem_bytes<Policy>();
   // once per device and kernel (one process may drive several devices)
   static std::atomic<uint64_t> configured{0};
   int dev = 0;
   CU_TRY(cudaGetDevice(&dev));
   if (!((configured.load(std::memory_order_relaxed) >> (dev & 63)) & 1ull)) {
-    CU_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, xmc::kSmemBytes));
+    CU_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured.fetch_or(1ull << (dev & 63));
   }
-  const int grid = grid_override > 0 ? grid_override : std::min(n_tiles, sm_count);
-  CU_TRY(launch_pdl(kern, grid, 64 + 32 * Policy::kEpiWarps, xmc::kSmemBytes, stream, a, b, p));
-  return XMC_OK;
-}
-
-// same, on CTA pairs (cluster of 2): n_tiles counts 256-row pair tiles
-template <class Policy>
-int launch_gemm2(const CUtensorMap& a, const CUtensorMap& b, const typename Policy::Params& p, int n_tiles,
-                 int sm_count, cudaStream_t stream, int pairs_override = 0) {
-  if (n_tiles <= 0) return XMC_OK;
-  auto kern = xmc::gemm2_kernel<Policy>;
-  CU_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, xmc::kSmem2Bytes));
-  const int pairs = pairs_override > 0 ? pairs_override : std::min(n_tiles, sm_count / 2);
-  kern<<<2 * pairs, 64 + 32 * Policy::kEpiWarps, xmc::kSmem2Bytes, stream>>>(a, b, p);
-  CU_TRY(cudaGetLastError());
+  if (Policy::kCTile && c == nullptr) return fail(XMC_ERR_STATE, "this kernel needs its epilogue-input tensor map");
+  int grid = grid_override > 0 ? grid_override : std::min(n_tiles, sm_count);
+  CU_TRY(launch_pdl(kern, grid, 64 + 32 * Policy::kEpiWarps, smem, stream, a, b, c ? *c : a, p));
   return XMC_OK;
 }
 
@@ -694,6 +682,10 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
       up.wd = wd;
       up.seed = seed;
       up.step = step;
+      for (int rd = 0; rd < 10; ++rd) {
+        up.rkey[rd][0] = (uint32_t)seed + (uint32_t)rd * 0x9E3779B9u;
+        up.rkey[rd][1] = (uint32_t)(seed >> 32) + (uint32_t)rd * 0xBB67AE85u;
+      }
       up.elem0 = (unsigned long long)(h->cfg.label_offset + row_base + s0) * (unsigned long long)d;
       up.round_dw_bf16 = (flags & XMC_STEP_ROUND_DW_BF16) ? 1 : 0;
       up.status = h->status;
@@ -711,11 +703,17 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
         up.kahan_rows = (int)std::min<int64_t>(h->kahan_rows - s0, rows_valid);
       }
       const bool rdw = up.round_dw_bf16 != 0, has_wd = wd != 0.f;
+      // the chunk's weights as the update epilogue's input: boxes of 128 rows x 128 bytes, 128-byte swizzle
+      CUtensorMap map_wt;
+      if (w8) {
+        if (int rc2 = make_map(&map_wt, true, wbase, d, rows_valid, d, 128, 128)) return rc2;
+      }
+      const CUtensorMap* wt = w8 ? &map_wt : nullptr;
 #define XMC_UPD(W8_, SR_, RD_, WD_) \
-  launch_gemm<xmc::UpdPolicy<W8_, SR_, RD_, WD_>>(map_g_k, map_xt, up, u_tiles, h->sm_count, st)
+  launch_gemm<xmc::UpdPolicy<W8_, SR_, RD_, WD_>>(map_g_k, map_xt, up, u_tiles, h->sm_count, st, 0, wt)
       if (kahan_here) {
-        rc = sr ? launch_gemm<xmc::UpdPolicy<true, true, false, false, true>>(map_g_k, map_xt, up, u_tiles, h->sm_count, st)
-                : launch_gemm<xmc::UpdPolicy<true, false, false, false, true>>(map_g_k, map_xt, up, u_tiles, h->sm_count, st);
+        rc = sr ? launch_gemm<xmc::UpdPolicy<true, true, false, false, true>>(map_g_k, map_xt, up, u_tiles, h->sm_count, st, 0, wt)
+                : launch_gemm<xmc::UpdPolicy<true, false, false, false, true>>(map_g_k, map_xt, up, u_tiles, h->sm_count, st, 0, wt);
       } else if (w8) {
         if (!rdw && !has_wd) rc = sr ? XMC_UPD(true, true, false, false) : XMC_UPD(true, false, false, false);
         else if (!rdw) rc = sr ? XMC_UPD(true, true, false, true) : XMC_UPD(true, false, false, true);
@@ -1016,9 +1014,19 @@ int xmc_large_k_matmul_noalloc(int32_t device, const void* a_bf16, const void* b
   return XMC_OK;
 }
 
+int xmc_test_sigmoid(int32_t device, const void* in_bf16, void* out_bf16, int32_t n, void* stream) {
+  if (in_bf16 == nullptr || out_bf16 == nullptr || n <= 0) return fail(XMC_ERR_INVALID, "bad argument");
+  DeviceGuard guard(device);
+  xmc::sigmoid_probe_kernel<<<cdiv(n, 256), 256, 0, (cudaStream_t)stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(in_bf16), reinterpret_cast<__nv_bfloat16*>(out_bf16), n);
+  CU_TRY(cudaGetLastError());
+  return XMC_OK;
+}
+
 int xmc_test_gemm(int32_t device, int32_t layout, int32_t dtype, int32_t M, int32_t N, int32_t K,
                   const void* A, const void* B, float* D, void* stream) {
   if (A == nullptr || B == nullptr || D == nullptr || M <= 0 || N <= 0 || K <= 0) return fail(XMC_ERR_INVALID, "bad argument");
+  if (layout < 0 || layout > 3) return fail(XMC_ERR_INVALID, "layout must be 0..3");
   if ((layout & 1) == 1 && dtype != XMC_DT_BF16) return fail(XMC_ERR_INVALID, "MN-major test takes bf16");
   if (dtype != XMC_DT_BF16 && dtype != XMC_DT_E4M3) return fail(XMC_ERR_INVALID, "dtype");
   DeviceGuard guard(device);
@@ -1026,9 +1034,6 @@ int xmc_test_gemm(int32_t device, int32_t layout, int32_t dtype, int32_t M, int3
   CU_TRY(cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, device));
   CU_TRY(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
   if (cc_major != 10) return fail(XMC_ERR_CUDA, "device is not sm_100");
-  // XMC_TEST_GEMM_REPEAT=n launches the contraction n times back to back (throughput probes)
-  const char* rep_env = getenv("XMC_TEST_GEMM_REPEAT");
-  const int repeat = rep_env ? std::max(1, atoi(rep_env)) : 1;
   int* status = nullptr;
   CU_TRY(cudaMalloc((void**)&status, 16));
   CU_TRY(cudaMemset(status, 0, 16));
@@ -1040,32 +1045,22 @@ int xmc_test_gemm(int32_t device, int32_t layout, int32_t dtype, int32_t M, int3
   p.n_ntiles = cdiv(N, 256);
   p.D = D;
   p.checksum_only = (layout & 2) ? 1 : 0;
-  const bool pair_mode = (layout & 4) != 0;
   layout &= 1;
-  if (pair_mode && layout == 1) { cudaFree(status); return fail(XMC_ERR_INVALID, "CTA pairs take K-major operands"); }
-  p.m_rows = pair_mode ? 256 : 128;
+  p.m_rows = 128;
   p.n_mtiles = cdiv(M, p.m_rows);
   p.status = status;
   int rc = XMC_OK;
   if (layout == 0) {
     if ((rc = make_map_kmajor(&ma, f8, A, K, M, K, 128))) { cudaFree(status); return rc; }
-    // a CTA of a pair stages only its half of the B rows
-    if ((rc = make_map_kmajor(&mb, f8, B, K, N, K, pair_mode ? 128 : 256))) { cudaFree(status); return rc; }
+    if ((rc = make_map_kmajor(&mb, f8, B, K, N, K, 256))) { cudaFree(status); return rc; }
     p.k_steps = cdiv((long long)K * (f8 ? 1 : 2), 128);
-    for (int r = 0; r < repeat && rc == XMC_OK; ++r) {
-      if (pair_mode)
-        rc = f8 ? launch_gemm2<xmc::PlainPolicy<true, false>>(ma, mb, p, p.n_mtiles * p.n_ntiles, sm_count, st)
-                : launch_gemm2<xmc::PlainPolicy<false, false>>(ma, mb, p, p.n_mtiles * p.n_ntiles, sm_count, st);
-      else
-        rc = f8 ? launch_gemm<xmc::PlainPolicy<true, false>>(ma, mb, p, p.n_mtiles * p.n_ntiles, sm_count, st)
-                : launch_gemm<xmc::PlainPolicy<false, false>>(ma, mb, p, p.n_mtiles * p.n_ntiles, sm_count, st);
-    }
+    rc = f8 ? launch_gemm<xmc::PlainPolicy<true, false>>(ma, mb, p, p.n_mtiles * p.n_ntiles, sm_count, st)
+            : launch_gemm<xmc::PlainPolicy<false, false>>(ma, mb, p, p.n_mtiles * p.n_ntiles, sm_count, st);
   } else {
     if ((rc = make_map_mnmajor(&ma, A, M, K, M))) { cudaFree(status); return rc; }
     if ((rc = make_map_mnmajor(&mb, B, N, K, N))) { cudaFree(status); return rc; }
     p.k_steps = cdiv(K, 64);
-    for (int r = 0; r < repeat && rc == XMC_OK; ++r)
-      rc = launch_gemm<xmc::PlainPolicy<false, true>>(ma, mb, p, p.n_mtiles * p.n_ntiles, sm_count, st);
+    rc = launch_gemm<xmc::PlainPolicy<false, true>>(ma, mb, p, p.n_mtiles * p.n_ntiles, sm_count, st);
   }
   if (rc == XMC_OK) {
     cudaError_t e = cudaStreamSynchronize(st);

@@ -20,7 +20,7 @@ struct NoState {};
 // the positives with set semantics (:108).
 // -------------------------------------------------------------------------------------------------
 struct FwdParams {
-  int m_rows;              // label rows per M tile: 128 (one CTA) or 256 (CTA pair)
+  int m_rows;              // label rows per M tile (128)
   int rows_valid;          // label rows of this scheduling chunk
   int n_ltiles, n_btiles;  // label tiles (128) x batch tiles (256)
   int batch, bpad;         // valid batch rows, padded row length of G (multiple of 16)
@@ -41,10 +41,11 @@ struct FwdPolicy {
   static constexpr bool kFp8 = FP8;
   static constexpr uint32_t kFmt = FP8 ? 0u : 1u;            // e4m3 | bf16
   static constexpr int kElemsPerRow = FP8 ? 128 : 64;
-#ifndef XMC_FWD_WARPS
-#define XMC_FWD_WARPS 8
-#endif
-  static constexpr int kEpiWarps = XMC_FWD_WARPS;
+  static constexpr int kEpiWarps = 8;
+  static constexpr int kStages = 4;
+  static constexpr bool kCTile = false;
+  static constexpr int kCBufs = 1;
+  static constexpr bool kBitmap = true;
   struct EpilogueState {
     float loss;
     int has_pos;
@@ -75,14 +76,14 @@ struct FwdPolicy {
     constexpr int kWordsPerRow = kTileN / 32;
     __syncwarp();
     for (int w = ec.lane; w < 32 * kWordsPerRow; w += 32) {
-      if ((w % kWordsPerRow) % ec.nsplit == ec.h) sh.bitmap[ec.q * 32 * kWordsPerRow + w] = 0u;
+      if ((w % kWordsPerRow) % ec.nsplit == ec.h) ec.bitmap[ec.q * 32 * kWordsPerRow + w] = 0u;
     }
     __syncwarp();
     for (int e = beg + ec.lane; e < end; e += 32) {
       const uint32_t ent = p.bucket_ent[e];
       const int lrow = (int)(ent >> 16), bl = (int)(ent & 0xFFFFu) - j.b0;
       if ((lrow >> 5) == ec.q && bl >= 0 && bl < kTileN && ((bl >> 5) % ec.nsplit) == ec.h)
-        atomicOr(&sh.bitmap[lrow * kWordsPerRow + (bl >> 5)], 1u << (bl & 31));
+        atomicOr(&ec.bitmap[lrow * kWordsPerRow + (bl >> 5)], 1u << (bl & 31));
     }
     __syncwarp();
   }
@@ -100,7 +101,7 @@ struct FwdPolicy {
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = 0u;
       }
-      const uint32_t bits = st.has_pos ? sh.bitmap[row * (kTileN / 32) + (c0 >> 5)] : 0u;
+      const uint32_t bits = st.has_pos ? ec.bitmap[row * (kTileN / 32) + (c0 >> 5)] : 0u;
       uint32_t out[16];
       // Per pair: one packed cvt rounds the logits to bf16, ex2 + rcp give the sigmoid, one packed cvt
       // rounds and packs it.  (cvt shares the special-function pipe with ex2/rcp; integer rounding
@@ -182,6 +183,8 @@ struct UpdParams {
   float lr_eff;            // lr / w_scale
   float wd;
   unsigned long long seed, step;
+  uint32_t rkey[10][2];       // Philox round keys (seed + round * Weyl constants), filled on the host: they sit in
+                              // the constant bank, so a round costs two multiplies and two 3-input xors
   unsigned long long elem0;   // global flat element index of W[0][0] of this chunk (Philox counter origin)
   int round_dw_bf16;
   // Kahan-compensated head rows (reference: fuse_kernel.py:202-287, chunked_head_kahan_fp8xmc_clf.py:127-131)
@@ -198,10 +201,17 @@ struct UpdPolicy {
   static constexpr bool kFp8 = false;
   static constexpr uint32_t kFmt = 1u;
   static constexpr int kElemsPerRow = 64;
-#ifndef XMC_UPD_WARPS
-#define XMC_UPD_WARPS 16
-#endif
-  static constexpr int kEpiWarps = XMC_UPD_WARPS;
+  static constexpr int kEpiWarps = 16;
+  // e4m3 weights: the tile's 128 x 256 weight bytes come in by TMA while the main loop runs and go back
+  // by TMA (two 32 KB slots, paid for with one operand stage: with a single slot the refill has to wait
+  // for the previous tile's store and the pipeline serialises -- measured 30 % slower); bf16 weights
+  // (64 KB per tile) are read from and written to global memory by the epilogue threads
+  static constexpr bool kCTile = W8;
+  static constexpr int kCBufs = 2;
+  static constexpr bool kBitmap = false;
+  static constexpr int kStages = W8 ? 3 : 4;
+  __device__ static int c_col(const Job& j) { return j.b0; }
+  __device__ static int c_row(const Job& j) { return j.a0; }
   static constexpr int kGroups = ((kTileN / 32) + (kEpiWarps / 4) - 1) / (kEpiWarps / 4);   // 32-column groups per thread and tile
   using EpilogueState = NoState;
 
@@ -229,39 +239,6 @@ struct UpdPolicy {
     }
   }
 
-  // 16 random bits for each of 32 consecutive elements starting at `elem` (multiple of 8): four
-  // Philox calls advanced round by round together so that their multiply chains overlap.
-  __device__ static void random32(const Params& p, unsigned long long elem, uint32_t (&r)[16]) {
-    constexpr uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
-    uint4 c[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const unsigned long long qi = (elem >> 3) + i;
-      c[i] = make_uint4((uint32_t)qi, (uint32_t)(qi >> 32), (uint32_t)p.step, (uint32_t)(p.step >> 32));
-    }
-    uint32_t k0 = (uint32_t)p.seed, k1 = (uint32_t)(p.seed >> 32);
-#pragma unroll
-    for (int rd = 0; rd < 10; ++rd) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        // one widening multiply yields both halves
-        const unsigned long long p0 = (unsigned long long)M0 * c[i].x;
-        const unsigned long long p1 = (unsigned long long)M1 * c[i].z;
-        c[i] = make_uint4((uint32_t)(p1 >> 32) ^ c[i].y ^ k0, (uint32_t)p1, (uint32_t)(p0 >> 32) ^ c[i].w ^ k1,
-                          (uint32_t)p0);
-      }
-      k0 += W0;
-      k1 += W1;
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      r[4 * i] = c[i].x; r[4 * i + 1] = c[i].y; r[4 * i + 2] = c[i].z; r[4 * i + 3] = c[i].w;
-    }
-  }
-  // element e (0..31) of the group takes half (e & 1) of word e >> 1
-  __device__ static uint32_t r16_of(const uint32_t (&r)[16], int e) {
-    return (e & 1) ? (r[e >> 1] >> 16) : (r[e >> 1] & 0xFFFFu);
-  }
   __device__ static float new_weight(const Params& p, float w, uint32_t acc_bits) {
     // no run-time branches in here: they would cut the per-element code into tiny basic blocks
     float a = __uint_as_float(acc_bits);
@@ -270,107 +247,188 @@ struct UpdPolicy {
     return fmaf(-p.lr_eff, a, w);
   }
 
-  // one 32-column group of one row: v = accumulators, w16[2] = the row's 32 e4m3 weights
-  __device__ static void process_w8(const Params& p, const uint32_t (&v)[32], const uint4 (&w16)[2],
-                                    unsigned long long elem, uint8_t* dst, bool store_lo, bool store_hi) {
-    uint32_t r[16];
-    if (SR) random32(p, elem, r);
-    U32x8 res;
+  // ------------------------------------------------------------------------------------------------
+  // e4m3 weights: eight consecutive elements of one row at a time -- one x8 accumulator load, 8 weight
+  // bytes of the shared-memory block, ONE Philox call (8 x 16 bits).  The body is small on purpose: it
+  // is looped, not unrolled, so that the epilogue's instruction stream stays resident in the instruction
+  // cache next to the single-thread producer and MMA loops that run beside it.
+  // ------------------------------------------------------------------------------------------------
+  __device__ static uint4 random8(const Params& p, unsigned long long elem) {
+    constexpr uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u;
+    const unsigned long long q = elem >> 3;
+    uint4 c = make_uint4((uint32_t)q, (uint32_t)(q >> 32), (uint32_t)p.step, (uint32_t)(p.step >> 32));
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const uint32_t rw[4] = {w16[h].x, w16[h].y, w16[h].z, w16[h].w};
-      uint32_t ow[4];
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {          // 4 elements per 32-bit word
-        float o[4];
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const float2 f = e4m3x2_to_float2((uint16_t)(rw[k] >> (16 * i)));
-          const int e = 16 * h + 4 * k + 2 * i;
-          o[2 * i] = new_weight(p, f.x, v[e]);
-          o[2 * i + 1] = new_weight(p, f.y, v[e + 1]);
-          if (SR) {
-            o[2 * i] = sr_e4m3(o[2 * i], r16_of(r, e));
-            o[2 * i + 1] = sr_e4m3(o[2 * i + 1], r16_of(r, e + 1));
-          }
-        }
-        ow[k] = (uint32_t)float2_to_e4m3x2(o[0], o[1]) | ((uint32_t)float2_to_e4m3x2(o[2], o[3]) << 16);
-      }
-      res.v[4 * h] = ow[0]; res.v[4 * h + 1] = ow[1]; res.v[4 * h + 2] = ow[2]; res.v[4 * h + 3] = ow[3];
+    for (int rd = 0; rd < 10; ++rd) {
+      const unsigned long long p0 = (unsigned long long)M0 * c.x;
+      const unsigned long long p1 = (unsigned long long)M1 * c.z;
+      c = make_uint4((uint32_t)(p1 >> 32) ^ c.y ^ p.rkey[rd][0], (uint32_t)p1, (uint32_t)(p0 >> 32) ^ c.w ^ p.rkey[rd][1],
+                     (uint32_t)p0);
     }
-    if (store_lo) st_global_256(dst, res);       // one whole sector per thread
+    return c;
+  }
+
+  // Fast path.  `bad` comes back true when stochastic rounding met a non-finite update (the bare
+  // add-and-mask would mangle a NaN pattern); the caller then redoes the eight with update8_careful.
+  // Detecting that costs one FMA-pipe add per element (a running sum of magnitudes) instead of a
+  // compare and a select each.
+  __device__ static uint2 update8(const Params& p, const uint32_t (&v)[8], uint2 wraw, uint4 r, bool& bad) {
+    const uint32_t rw[2] = {wraw.x, wraw.y};
+    const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
+    uint32_t ow[2];
+    float mag = 0.f;
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {            // 4 elements per 32-bit word
+      float o[4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const float2 f = e4m3x2_to_float2((uint16_t)(rw[k] >> (16 * i)));
+        const int e = 4 * k + 2 * i;
+        o[2 * i] = new_weight(p, f.x, v[e]);
+        o[2 * i + 1] = new_weight(p, f.y, v[e + 1]);
+        if (SR) {
+          // both elements of a pair draw from the same Philox word: element j takes half (j & 1) of word j >> 1
+          const uint32_t w32 = rr[e >> 1];
+          const float x0 = o[2 * i] * kSrDown, x1 = o[2 * i + 1] * kSrDown;
+          mag += fabsf(x0);
+          mag += fabsf(x1);
+          const uint32_t b0 = (__float_as_uint(x0) + ((w32 & 0xFFFFu) << 4)) & 0xFFF00000u;
+          const uint32_t b1 = (__float_as_uint(x1) + ((w32 >> 16) << 4)) & 0xFFF00000u;
+          o[2 * i] = __uint_as_float(b0) * kSrUp;
+          o[2 * i + 1] = __uint_as_float(b1) * kSrUp;
+        }
+      }
+      ow[k] = (uint32_t)float2_to_e4m3x2(o[0], o[1]) | ((uint32_t)float2_to_e4m3x2(o[2], o[3]) << 16);
+    }
+    bad = SR && !(mag < 1.0e30f);              // an Inf or NaN among the eight (finite updates sum to < 2^12 here)
+    return make_uint2(ow[0], ow[1]);
+  }
+
+  // The same eight, element by element with the NaN-preserving rounding (rare).
+  __device__ __noinline__ static uint2 update8_careful(const Params& p, uint32_t v0, uint32_t v1, uint32_t v2, uint32_t v3,
+                                                       uint32_t v4, uint32_t v5, uint32_t v6, uint32_t v7, uint2 wraw, uint4 r) {
+    const uint32_t v[8] = {v0, v1, v2, v3, v4, v5, v6, v7};
+    const uint32_t rw[2] = {wraw.x, wraw.y};
+    const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
+    uint32_t ow[2] = {0u, 0u};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float w = e4m3x2_to_float2((uint16_t)(rw[e >> 2] >> (8 * (e & 3)))).x;
+      const uint32_t r16 = (e & 1) ? (rr[e >> 1] >> 16) : (rr[e >> 1] & 0xFFFFu);
+      const float o = sr_e4m3(new_weight(p, w, v[e]), r16);
+      ow[e >> 2] |= ((uint32_t)float2_to_e4m3x2(o, 0.f) & 0xFFu) << (8 * (e & 3));
+    }
+    return make_uint2(ow[0], ow[1]);
   }
 
   // Kahan-compensated rows: w = W + D - lr*acc; W' = round(w); D' = cast(D + W - W' - lr*acc)
   // (fuse_kernel.py:253-273).  Not on the fast path: only the head rows of chunk 0 come here.
-  __device__ static void process_w8_kahan(const Params& p, const uint32_t (&v)[32], const uint4 (&w16)[2],
-                                          unsigned long long elem, uint8_t* dst, void* krow, bool store_lo,
-                                          bool store_hi) {
-    uint32_t r[16];
-    if (SR) random32(p, elem, r);
-#pragma unroll 1
-    for (int h = 0; h < 2; ++h) {
-      if (!(h == 0 ? store_lo : store_hi)) continue;
-      float dv[16];
-      if (p.kahan_e5m2) {
-        const uint4 raw = reinterpret_cast<const uint4*>(krow)[h];
-        const uint32_t rk[4] = {raw.x, raw.y, raw.z, raw.w};
+  // krow: the row's 8 compensation values (bf16: 16 bytes, e5m2: 8 bytes), updated in place.
+  __device__ __noinline__ static uint2 update8_kahan(const Params& p, uint32_t v0, uint32_t v1, uint32_t v2, uint32_t v3,
+                                                     uint32_t v4, uint32_t v5, uint32_t v6, uint32_t v7, uint2 wraw, uint4 r,
+                                                     void* krow) {
+    const uint32_t v[8] = {v0, v1, v2, v3, v4, v5, v6, v7};
+    const uint32_t rw[2] = {wraw.x, wraw.y};
+    const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
+    float dv[8];
+    if (p.kahan_e5m2) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(krow);
+      const uint32_t rk[2] = {raw.x, raw.y};
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(rk[i >> 1] >> (16 * (i & 1))), __NV_E5M2);
-          const float2 f = __half22float2(*reinterpret_cast<__half2*>(&hr));
-          dv[2 * i] = f.x; dv[2 * i + 1] = f.y;
-        }
-      } else {
-#pragma unroll
-        for (int g = 0; g < 2; ++g) {
-          const uint4 raw = reinterpret_cast<const uint4*>(krow)[2 * h + g];
-          const uint32_t rk[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            dv[8 * g + 2 * i] = bf16_bits_to_float(rk[i] & 0xFFFFu);
-            dv[8 * g + 2 * i + 1] = bf16_bits_to_float(rk[i] >> 16);
-          }
-        }
+      for (int i = 0; i < 4; ++i) {
+        __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(rk[i >> 1] >> (16 * (i & 1))), __NV_E5M2);
+        const float2 f = __half22float2(*reinterpret_cast<__half2*>(&hr));
+        dv[2 * i] = f.x; dv[2 * i + 1] = f.y;
       }
-      const uint32_t rw[4] = {w16[h].x, w16[h].y, w16[h].z, w16[h].w};
-      uint32_t ow[4];
-      float dn[16];
+    } else {
+      const uint4 raw = *reinterpret_cast<const uint4*>(krow);
+      const uint32_t rk[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {          // pairs
-        const float2 f = e4m3x2_to_float2((uint16_t)(rw[k >> 1] >> (16 * (k & 1))));
-        const float wv[2] = {f.x, f.y};
-        float on[2];
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const int e = 16 * h + 2 * k + i;
-          const float a = __uint_as_float(v[e]);
-          float o = fmaf(-p.lr_eff, a, __fadd_rn(wv[i], dv[2 * k + i]));
-          if (SR) o = sr_e4m3(o, r16_of(r, e));
-          else o = e4m3x2_to_float2(float2_to_e4m3x2(o, 0.f)).x;       // the value W' will hold
-          on[i] = o;
-          dn[2 * k + i] = __fsub_rn(__fsub_rn(__fadd_rn(dv[2 * k + i], wv[i]), o), __fmul_rn(p.lr_eff, a));
-        }
-        const uint32_t pair = float2_to_e4m3x2(on[0], on[1]);
-        if (k & 1) ow[k >> 1] |= pair << 16; else ow[k >> 1] = pair;
-      }
-      *reinterpret_cast<uint4*>(dst + 16 * h) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
-      if (p.kahan_e5m2) {
-        uint32_t ok[4];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const uint32_t pr = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(dn[2 * i], dn[2 * i + 1]), __NV_NOSAT, __NV_E5M2);
-          if (i & 1) ok[i >> 1] |= pr << 16; else ok[i >> 1] = pr;
-        }
-        reinterpret_cast<uint4*>(krow)[h] = make_uint4(ok[0], ok[1], ok[2], ok[3]);
-      } else {
-#pragma unroll
-        for (int g = 0; g < 2; ++g)
-          reinterpret_cast<uint4*>(krow)[2 * h + g] =
-              make_uint4(pack_bf16x2(dn[8 * g], dn[8 * g + 1]), pack_bf16x2(dn[8 * g + 2], dn[8 * g + 3]),
-                         pack_bf16x2(dn[8 * g + 4], dn[8 * g + 5]), pack_bf16x2(dn[8 * g + 6], dn[8 * g + 7]));
+      for (int i = 0; i < 4; ++i) {
+        dv[2 * i] = bf16_bits_to_float(rk[i] & 0xFFFFu);
+        dv[2 * i + 1] = bf16_bits_to_float(rk[i] >> 16);
       }
     }
+    uint32_t ow[2] = {0u, 0u};
+    float dn[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float wv = e4m3x2_to_float2((uint16_t)(rw[e >> 2] >> (8 * (e & 3)))).x;
+      const float a = __uint_as_float(v[e]);
+      float o = fmaf(-p.lr_eff, a, __fadd_rn(wv, dv[e]));
+      if (SR) o = sr_e4m3(o, (e & 1) ? (rr[e >> 1] >> 16) : (rr[e >> 1] & 0xFFFFu));
+      const uint32_t byte = (uint32_t)float2_to_e4m3x2(o, 0.f) & 0xFFu;
+      o = e4m3x2_to_float2((uint16_t)byte).x;                       // the value W' holds
+      ow[e >> 2] |= byte << (8 * (e & 3));
+      dn[e] = __fsub_rn(__fsub_rn(__fadd_rn(dv[e], wv), o), __fmul_rn(p.lr_eff, a));
+    }
+    if (p.kahan_e5m2) {
+      uint32_t ok[2];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t pr = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(dn[2 * i], dn[2 * i + 1]), __NV_NOSAT, __NV_E5M2);
+        if (i & 1) ok[i >> 1] |= pr << 16; else ok[i >> 1] = pr;
+      }
+      *reinterpret_cast<uint2*>(krow) = make_uint2(ok[0], ok[1]);
+    } else {
+      *reinterpret_cast<uint4*>(krow) = make_uint4(pack_bf16x2(dn[0], dn[1]), pack_bf16x2(dn[2], dn[3]),
+                                                   pack_bf16x2(dn[4], dn[5]), pack_bf16x2(dn[6], dn[7]));
+    }
+    return make_uint2(ow[0], ow[1]);
+  }
+
+  // the whole tile for e4m3 weights: 4 * kGroups sub-blocks of 8 columns per thread
+  __device__ static void epilogue_w8(const Params& p, const Job& j, uint32_t taddr, bool have_acc, const EpiCtx& ec) {
+    const int row = ec.q * 32 + ec.lane;
+    const int crow = j.a0 + row;
+    const bool row_valid = crow < p.rows_valid;
+    const unsigned long long erow = p.elem0 + (unsigned long long)crow * p.d + j.b0;
+#pragma unroll 1
+    for (int sb = 0; sb < 4 * kGroups; ++sb) {
+      const int c0 = 32 * (ec.h + ec.nsplit * (sb >> 2)) + 8 * (sb & 3);
+      if (c0 >= j.n_eff) break;                          // warp-uniform
+      // tcgen05.ld / wait::ld are warp-wide (.sync.aligned): issued by all 32 lanes, outside every
+      // lane-dependent branch; the load is asynchronous, so the random bits are drawn while it flies
+      uint32_t v[8];
+      if (have_acc) {
+        tmem_ld8(taddr + c0, v);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = 0u;
+      }
+      uint2* wslot = ctile_ptr8(ec.ctile, row, c0);
+      const uint2 wraw = *wslot;                         // rows / columns outside the tensor were zero-filled
+      uint4 r = make_uint4(0u, 0u, 0u, 0u);
+      if (SR) r = random8(p, erow + c0);
+      if (have_acc) tmem_ld_wait_for(v);
+      uint2 out;
+      bool bad = false;
+      bool kahan_row = false;
+      if constexpr (KAHAN) kahan_row = crow < p.kahan_rows;
+      if (kahan_row) {
+        out = wraw;
+        if (row_valid && j.b0 + c0 < p.d) {
+          uint8_t* krow = reinterpret_cast<uint8_t*>(p.kahan) + ((size_t)crow * p.d + j.b0 + c0) * (p.kahan_e5m2 ? 1 : 2);
+          out = update8_kahan(p, v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7], wraw, r, krow);
+        }
+      } else {
+        out = update8(p, v, wraw, r, bad);
+        if (bad) out = update8_careful(p, v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7], wraw, r);
+      }
+      if (row_valid) *wslot = out;                       // in place; the engine stores the block back with TMA
+    }
+  }
+
+  // 16 random bits for each of 32 consecutive elements starting at `elem` (bf16 weights): four Philox
+  // calls, element e of the 32 takes half (e & 1) of word e >> 1
+  __device__ static void random32(const Params& p, unsigned long long elem, uint32_t (&r)[16]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint4 c = random8(p, elem + 8 * i);
+      r[4 * i] = c.x; r[4 * i + 1] = c.y; r[4 * i + 2] = c.z; r[4 * i + 3] = c.w;
+    }
+  }
+  __device__ static uint32_t r16_of(const uint32_t (&r)[16], int e) {
+    return (e & 1) ? (r[e >> 1] >> 16) : (r[e >> 1] & 0xFFFFu);
   }
 
   __device__ static void process_bf16(const Params& p, const uint32_t (&v)[32], unsigned long long elem,
@@ -396,39 +454,19 @@ struct UpdPolicy {
 
   __device__ static void epilogue(const Params& p, const Job& j, uint32_t taddr, bool have_acc,
                                   SharedTail&, const EpiCtx& ec, EpilogueState& st) {
-    const int row = ec.q * 32 + ec.lane;
-    const int crow = j.a0 + row;
-    const bool row_valid = crow < p.rows_valid;
-    const unsigned long long erow = p.elem0 + (unsigned long long)crow * p.d + j.b0;
-    // One group body in the instruction stream (the unrolled form overflowed the instruction cache and
-    // the register file); latency is hidden by running 16 epilogue warps instead.
-    uint32_t v[32];
+    if constexpr (W8) {
+      epilogue_w8(p, j, taddr, have_acc, ec);
+    } else {
+      const int row = ec.q * 32 + ec.lane;
+      const int crow = j.a0 + row;
+      const bool row_valid = crow < p.rows_valid;
+      const unsigned long long erow = p.elem0 + (unsigned long long)crow * p.d + j.b0;
+      uint32_t v[32];
 #pragma unroll 1
-    for (int g = 0; g < kGroups; ++g) {
-      const int c0 = 32 * (ec.h + ec.nsplit * g);
-      if (c0 >= j.n_eff) break;
-      const int col = j.b0 + c0;
-      if constexpr (W8) {
-        uint8_t* wp = reinterpret_cast<uint8_t*>(p.W) + (size_t)crow * p.d + col;
-        uint4 w16[2];
-        {
-          // d is a multiple of 64 and col of 32: the 32-byte segment is inside the row or absent
-          U32x8 raw;
-          if (row_valid && col < p.d) raw = ld_global_256(wp);
-          else raw = U32x8{{0, 0, 0, 0, 0, 0, 0, 0}};
-          w16[0] = make_uint4(raw.v[0], raw.v[1], raw.v[2], raw.v[3]);
-          w16[1] = make_uint4(raw.v[4], raw.v[5], raw.v[6], raw.v[7]);
-        }
-        load_acc(taddr + c0, have_acc, v);
-        if constexpr (KAHAN) {
-          if (row_valid && crow < p.kahan_rows) {
-            uint8_t* krow = reinterpret_cast<uint8_t*>(p.kahan) + ((size_t)crow * p.d + col) * (p.kahan_e5m2 ? 1 : 2);
-            process_w8_kahan(p, v, w16, erow + c0, wp, krow, col < p.d, col + 16 < p.d);
-            continue;
-          }
-        }
-        if (row_valid) process_w8(p, v, w16, erow + c0, wp, col < p.d, col + 16 < p.d);
-      } else {
+      for (int g = 0; g < kGroups; ++g) {
+        const int c0 = 32 * (ec.h + ec.nsplit * g);
+        if (c0 >= j.n_eff) break;
+        const int col = j.b0 + c0;
         __nv_bfloat16* wp = reinterpret_cast<__nv_bfloat16*>(p.W) + (size_t)crow * p.d + col;
         load_acc(taddr + c0, have_acc, v);
         if (row_valid) process_bf16(p, v, erow + c0, wp, col + 16 < p.d ? 2 : (col < p.d ? 1 : 0));
@@ -462,6 +500,10 @@ struct LogitsPolicy {
   static constexpr uint32_t kFmt = FP8 ? 0u : 1u;
   static constexpr int kElemsPerRow = FP8 ? 128 : 64;
   static constexpr int kEpiWarps = 8;
+  static constexpr int kStages = 4;
+  static constexpr bool kCTile = false;
+  static constexpr int kCBufs = 1;
+  static constexpr bool kBitmap = false;
   using EpilogueState = NoState;
   __device__ static int num_tiles(const Params& p) { return p.n_mtiles * p.n_ntiles; }
   __device__ static void job(const Params& p, int tile, Job& j) {
@@ -564,6 +606,10 @@ struct TopkPolicy {
   static constexpr uint32_t kFmt = FP8 ? 0u : 1u;
   static constexpr int kElemsPerRow = FP8 ? 128 : 64;
   static constexpr int kEpiWarps = 8;
+  static constexpr int kStages = 4;
+  static constexpr bool kCTile = false;
+  static constexpr int kCBufs = 1;
+  static constexpr bool kBitmap = false;
   struct EpilogueState {
     float thr;             // own threshold
     float g;               // published threshold of the row (refreshed per tile)
@@ -776,7 +822,7 @@ struct TopkPolicy {
 // Plain D = A B^T, fp32 out (engine self-test; also the logits kernel's skeleton)
 // -------------------------------------------------------------------------------------------------
 struct PlainParams {
-  int m_rows;              // rows per M tile: 128 (one CTA) or 256 (CTA pair)
+  int m_rows;              // rows per M tile (128)
   int M, N;
   int n_mtiles, n_ntiles;
   int k_steps;
@@ -793,6 +839,10 @@ struct PlainPolicy {
   static constexpr uint32_t kFmt = FP8 ? 0u : 1u;
   static constexpr int kElemsPerRow = FP8 ? 128 : 64;
   static constexpr int kEpiWarps = 8;
+  static constexpr int kStages = 4;
+  static constexpr bool kCTile = false;
+  static constexpr int kCBufs = 1;
+  static constexpr bool kBitmap = false;
   using EpilogueState = NoState;
   __device__ static int num_tiles(const Params& p) { return p.n_mtiles * p.n_ntiles; }
   __device__ static void job(const Params& p, int tile, Job& j) {

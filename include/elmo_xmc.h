@@ -181,11 +181,17 @@ int xmc_large_k_matmul_noalloc(int32_t device, const void* a_bf16, const void* b
  *   layout 0: A [M x K], B [N x K] both K-major (row-major as written), dtype XMC_DT_BF16 or XMC_DT_E4M3
  *   layout 1: A given as [K x M], B as [K x N] row-major (both "MN-major"), dtype XMC_DT_BF16
  *   layout | 2: same contraction, but D is not stored (times the main loop alone)
- *   layout | 4: layout 0 on CTA pairs (cluster of two, tcgen05 cta_group::2)
  * M, N, K arbitrary positive (rows 16-byte aligned: inner extents multiples of 8 (bf16) / 16 (e4m3)).
  */
 int xmc_test_gemm(int32_t device, int32_t layout, int32_t dtype, int32_t M, int32_t N, int32_t K,
                   const void* A, const void* B, float* D, void* stream);
+
+/*
+ * Test hook: out[i] = bf16(sigmoid(in[i])) for n bf16 values, computed exactly as the forward kernel's
+ * epilogue computes the logit gradient (reference: torch.sigmoid on the bf16 logits,
+ * src/xmc_classifiers/chunked_fp8xmc_clf.py:107).  Lets a test sweep all 65 536 bf16 inputs.
+ */
+int xmc_test_sigmoid(int32_t device, const void* in_bf16, void* out_bf16, int32_t n, void* stream);
 
 #ifdef __cplusplus
 }

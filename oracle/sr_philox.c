@@ -55,7 +55,7 @@ void oracle_sr_e4m3(const float* w, uint64_t n, uint64_t first_elem, uint64_t se
     y = u2f((f2u(y) + (r << 4)) & 0xFFF00000u);
     if (small) y -= 0.015625f;
     y = fminf(y, 448.0f);
-    out[i] = y == 0.0f ? 0.0f : copysignf(y, x);     /* a zero result is +0 */
+    out[i] = copysignf(y, x);                         /* the sign is kept, also for a zero result */
   }
 }
 

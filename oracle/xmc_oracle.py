@@ -124,7 +124,9 @@ def sr_e4m3_exact(w: np.ndarray, r16: np.ndarray) -> np.ndarray:
     fuse_kernel.py:28-36).  Below 2^-6 the e4m3 grid is uniform with step 2^-9, which the bit
     trick does not see (its final convert re-rounds to nearest); adding 2^-6 first moves the
     value into the binade [2^-6, 2^-5) whose 3-bit step is exactly 2^-9, and subtracting it
-    afterwards is exact.  A zero result is +0.  Result is returned as fp32 values on the e4m3 grid.
+    afterwards is exact.  The sign of w is kept, also when the result is zero (as the reference's
+    trick does).  The CUDA kernel reaches the same bits by scaling with 2^-120 into fp32's own
+    subnormal range.  Result is returned as fp32 values on the e4m3 grid.
     """
     w = np.asarray(w, dtype=np.float32)
     nan = np.isnan(w)
@@ -137,7 +139,6 @@ def sr_e4m3_exact(w: np.ndarray, r16: np.ndarray) -> np.ndarray:
     y = np.where(small, y - np.float32(2.0 ** -6), y).astype(np.float32)
     y = np.minimum(y, np.float32(E4M3_MAX))
     out = np.copysign(y, w).astype(np.float32)
-    out[out == 0] = 0.0                      # a zero result is written as +0
     out[nan] = np.nan
     return out
 

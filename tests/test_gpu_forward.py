@@ -134,3 +134,24 @@ def test_checkpoint_round_trip_continues_the_same_stochastic_stream():
         assert torch.equal(pa.data.view(torch.uint8), pb.data.view(torch.uint8))
     assert torch.equal(a.grad_input, b.grad_input)
     a._handle.check(); b._handle.check()
+
+
+def test_sigmoid_of_every_bf16_input():
+    """The epilogue's sigmoid (approximate ex2 + rcp, rounded to bf16) against torch.sigmoid on bf16
+    (chunked_fp8xmc_clf.py:107) for all 65 536 bf16 bit patterns."""
+    import ctypes as C
+    from elmo_b200 import _lib
+    lib = _lib.load()
+    bits = torch.arange(65536, dtype=torch.int32).to(torch.uint16)
+    x = bits.view(torch.bfloat16)
+    want = torch.sigmoid(x.float()).to(torch.bfloat16)
+    xd = x.cuda()
+    out = torch.empty_like(xd)
+    _lib.check(lib.xmc_test_sigmoid(0, C.c_void_p(xd.data_ptr()), C.c_void_p(out.data_ptr()), 65536,
+                                    C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    got = out.cpu()
+    ok = ~torch.isnan(x.float())
+    same = (got.view(torch.int16) == want.view(torch.int16))[ok]
+    # flush-to-zero of the approximate ops may turn a result below 2^-126 into 0: allow those
+    tiny = want.float().abs()[ok] < 2.0 ** -120
+    assert bool((same | tiny).all()), int((~(same | tiny)).sum())

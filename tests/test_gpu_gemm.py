@@ -39,15 +39,3 @@ def test_mnmajor_bf16(m, n, k):
     d = test_gemm(a, b, 1)
     ref = a.float().t() @ b.float()
     assert torch.allclose(d, ref, rtol=1e-4, atol=2e-3), float((d - ref).abs().max())
-
-
-@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float8_e4m3fn])
-@pytest.mark.parametrize("m,n,k", [(256, 256, 128), (512, 768, 1024), (300, 80, 400), (1000, 528, 768), (64, 16, 128)])
-def test_kmajor_cta_pairs(m, n, k, dtype):
-    """The same contraction on CTA pairs (cluster of two, cta_group::2)."""
-    from elmo_b200.handle import test_gemm
-    g = torch.Generator().manual_seed(m + n + k)
-    a = _rand((m, k), dtype, g); b = _rand((n, k), dtype, g)
-    d = test_gemm(a, b, 4)
-    ref = a.float() @ b.float().t()
-    assert torch.allclose(d, ref, rtol=1e-4, atol=1e-3), float((d - ref).abs().max())

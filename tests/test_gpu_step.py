@@ -93,6 +93,26 @@ def test_fp8_step_large_batch(B):
     assert abs(loss - want_loss) < 1e-3 * abs(want_loss)
 
 
+def test_fp8_step_nonfinite_weights_sr():
+    """A NaN weight stays NaN under stochastic rounding (its whole label row turns NaN, as in the
+    reference's arithmetic) and updates that leave +-448 saturate; all other rows are unaffected."""
+    from oracle import xmc_oracle as O
+    L, d, B = 512, 128, 32
+    w, x, lab = _inputs(L, d, B, 100, seed=4)
+    w = w.clone()
+    w.view(torch.uint8)[37, 5] = 0x7F                      # e4m3 NaN
+    w[200:204] = torch.full((4, d), 448.0).to(E4M3)
+    w[204:208] = torch.full((4, d), -448.0).to(E4M3)
+    want_w, _, _ = O.fp8_chunked_step([w], x, lab, 3000.0, rounding="sr", seed=5, step=1)
+    got_w, _, _, _ = _run_gpu("fp8", [w], x, lab, 3000.0, stochastic=True, step=1, sched=256)
+    got, want = got_w[0], want_w[0]
+    assert torch.equal(torch.isnan(got.float()), torch.isnan(want.float()))
+    assert bool(torch.isnan(got.float()[37]).all()) and int(torch.isnan(got.float()).sum()) == d
+    finite = ~torch.isnan(got.float())
+    assert float(got.float()[finite].abs().max()) == 448.0
+    assert frac_equal_bits(got[finite], want[finite]) >= 0.999      # (a NaN's sign bit is not compared)
+
+
 def test_fp8_step_with_subnormal_weights():
     """Most stored weights below 2^-6 (e4m3 subnormals): exercises the in-kernel e4m3 -> bf16
     operand conversion of grad_X and stochastic rounding on the uniform part of the grid."""
