@@ -47,6 +47,7 @@ _SIGNATURES = {
     "xmc_version": (C.c_char_p, []),
     "xmc_large_k_matmul_noalloc": (C.c_int, [C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
                                              C.c_int32, C.c_void_p, C.c_void_p]),
+    "xmc_noalloc_check": (C.c_int, [C.c_int32, C.c_void_p]),
     "xmc_test_sigmoid": (C.c_int, [C.c_int32, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p]),
     "xmc_test_gemm": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                 C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),

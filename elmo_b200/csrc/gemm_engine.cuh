@@ -109,6 +109,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       mbar_init(smem_u32(&sh.c_empty[b]), 1);
     }
     sh.ctl.abort = 0;
+    sh.ctl.limit = Policy::wait_limit(p);
     fence_barrier_init();
     tma_prefetch_desc(&map_a);
     tma_prefetch_desc(&map_b);
@@ -169,7 +170,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           const uint32_t sa = stage0 + s * kStageBytes;
           const uint32_t sb = sa + kStageABytes;
           if constexpr (!Policy::kMnMajor) {
-            if (elect_one()) {
+            if (!Policy::skip_load(p, tile, k) && elect_one()) {
               mbar_arrive_expect_tx(bar, kStageBytes);
               tma_load_2d(sa, &map_a, bar, kk, job.a0);
               tma_load_2d(sb, &map_b, bar, kk, job.b0);

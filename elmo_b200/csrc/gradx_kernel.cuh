@@ -98,6 +98,7 @@ gradx_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant__ 
     }
     mbar_init(smem_u32(&sh.tmem_full), 1);
     sh.ctl.abort = 0;
+    sh.ctl.limit = kWaitLimitCycles;
     fence_barrier_init();
     tma_prefetch_desc(&map_g);
     tma_prefetch_desc(&map_w);

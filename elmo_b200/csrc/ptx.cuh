@@ -24,6 +24,7 @@ enum : int {
 
 struct Ctl {                 // lives in shared memory, one per CTA
   volatile int abort;
+  long long limit;           // cycles any single wait of this CTA may last (kWaitLimitCycles unless a test shortens it)
 };
 
 __device__ __forceinline__ void report(int* status, int code, int info) {
@@ -91,7 +92,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Wait limit for any single mbarrier wait, in SM clock cycles (~2 s at 2 GHz).  Far above any
+// Default limit of any single mbarrier wait, in SM clock cycles (~2 s at 2 GHz).  Far above any
 // legitimate wait (a whole kernel here runs for well under 100 ms) and far below a watchdog.
 // The SM-local cycle counter is used because it is cheap to read: waits sit on the critical path
 // of the producer/MMA hand-off, and the global nanosecond timer costs about a microsecond per read.
@@ -108,7 +109,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Ctl* ct
     ++spins;
     if ((spins & 255u) == 0u) {
       if (ctl->abort) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
+      if (clock64() - t0 > ctl->limit) {
         ctl->abort = 1;
         report(status, DEV_WAIT_TIMEOUT, where);
         return false;
@@ -138,7 +139,7 @@ __device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity,
     ++spins;
     if ((spins & 63u) == 0u) {
       if (ctl->abort) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
+      if (clock64() - t0 > ctl->limit) {
         ctl->abort = 1;
         report(status, DEV_WAIT_TIMEOUT, where);
         return false;

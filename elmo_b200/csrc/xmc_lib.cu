@@ -383,7 +383,9 @@ int xmc_create(const xmc_config* cfg, xmc_handle** out) {
     xmc_destroy(h);
     return rc;
   }
-  // per-process L2 carve-out for the partial sums (a context limit: it ends with the process)
+  // L2 carve-out for the partial sums: cudaLimitPersistingL2CacheSize is a limit of the whole CUDA
+  // context, so other kernels of the process see that much less L2 while it is set (documented in the
+  // header; XMC_NO_L2_PERSIST=1 in the environment leaves the limit alone)
   if (getenv("XMC_NO_L2_PERSIST") == nullptr && prop.persistingL2CacheMaxSize > 0) {
     const size_t want = std::min<size_t>((size_t)h->partial_floats * 4, (size_t)prop.persistingL2CacheMaxSize);
     if (cudaDeviceSetLimit(cudaLimitPersistingL2CacheSize, want) == cudaSuccess) h->l2_persist_bytes = (int64_t)want;
@@ -396,6 +398,7 @@ int xmc_create(const xmc_config* cfg, xmc_handle** out) {
 int xmc_destroy(xmc_handle* h) {
   if (h == nullptr) return XMC_OK;
   DeviceGuard guard(h->cfg.device);
+  if (h->l2_persist_bytes > 0) cudaCtxResetPersistingL2Cache();   // lines pinned for the partial sums become normal again
   void* ptrs[] = {h->x8, h->x16, h->xt, h->G, h->w16, h->partial, h->bucket_cnt, h->bucket_off,
                   h->entries, h->loss_partial, h->status, h->topk_val, h->topk_idx, h->topk_cnt, h->topk_thr, h->topk_max, h->topk_row};
   for (void* p : ptrs)
@@ -744,6 +747,12 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
     xmc::reduce_loss_kernel<<<1, 32, 0, st>>>(h->loss_partial, launch_idx * h->sm_count * xmc::kMaxEpiWarps, loss_out);
     CU_TRY(cudaGetLastError());
   }
+  if (h->l2_persist_bytes > 0) {
+    // the caller's stream leaves this call without the window (kernels launched after it are unaffected)
+    cudaStreamAttrValue attr;
+    memset(&attr, 0, sizeof(attr));
+    CU_TRY(cudaStreamSetAttribute(st, cudaStreamAttributeAccessPolicyWindow, &attr));
+  }
   mark(h, K_END, st);
   return XMC_OK;
 }
@@ -954,7 +963,7 @@ static __device__ __align__(256) float g_noalloc_scratch[kNoAllocFloats + 64];
 // Device addresses of the array, one per device, filled on the first call for that device.  In host
 // code the symbol itself is only a stand-in; the address a kernel can use comes from
 // cudaGetSymbolAddress with the device current.
-static float* g_noalloc_ptr[kNoAllocMaxDevices] = {nullptr};
+static std::atomic<float*> g_noalloc_ptr[kNoAllocMaxDevices];
 }  // namespace
 
 int xmc_large_k_matmul_noalloc(int32_t device, const void* a_bf16, const void* b, int32_t b_dtype,
@@ -966,10 +975,11 @@ int xmc_large_k_matmul_noalloc(int32_t device, const void* a_bf16, const void* b
   if ((size_t)m * (size_t)n > kNoAllocFloats)
     return fail(XMC_ERR_INVALID, "m*n = %lld exceeds the built-in scratch of %lld floats (8 MiB): use the handle-based API",
                 (long long)m * n, (long long)kNoAllocFloats);
-  if (((uintptr_t)c_f32 & 15u) != 0) return fail(XMC_ERR_INVALID, "c must be 16-byte aligned");
+  if (((uintptr_t)c_f32 & 15u) != 0 || ((uintptr_t)a_bf16 & 15u) != 0 || ((uintptr_t)b & 15u) != 0)
+    return fail(XMC_ERR_INVALID, "a, b and c must be 16-byte aligned");
   if (device < 0 || device >= kNoAllocMaxDevices) return fail(XMC_ERR_INVALID, "device %d out of range", device);
   DeviceGuard guard(device);
-  if (g_noalloc_ptr[device] == nullptr) {
+  if (g_noalloc_ptr[device].load(std::memory_order_acquire) == nullptr) {
     // set-up, once per device, with that device current (the guard above)
     int cc_major = 0;
     CU_TRY(cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, device));
@@ -978,9 +988,10 @@ int xmc_large_k_matmul_noalloc(int32_t device, const void* a_bf16, const void* b
     CU_TRY(cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch));
     CU_TRY(cudaFuncSetAttribute(xmc::gradx_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, xmc::kGxSmemBytes));
     CU_TRY(cudaFuncSetAttribute(xmc::gradx_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, xmc::kGxSmemBytes));
-    g_noalloc_ptr[device] = ptr;
+    // two threads racing through the set-up compute the same address; the publication itself is atomic
+    g_noalloc_ptr[device].store(ptr, std::memory_order_release);
   }
-  float* scratch = g_noalloc_ptr[device];
+  float* scratch = g_noalloc_ptr[device].load(std::memory_order_acquire);
   int* status = reinterpret_cast<int*>(scratch + kNoAllocFloats);
   int sm_count = 0;
   CU_TRY(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
@@ -1000,10 +1011,10 @@ int xmc_large_k_matmul_noalloc(int32_t device, const void* a_bf16, const void* b
   gp.total_ksteps = cdiv(k, xmc::kGxRows);
   n_splits = std::max(1, std::min(n_splits, gp.total_ksteps));
   gp.n_splits = n_splits;
-  gp.accumulate = 0;            // every slot in use is fully overwritten: nothing to clear but the status
+  gp.accumulate = 0;            // every slot in use is fully overwritten: nothing has to start at zero
   gp.partial = scratch;
-  gp.status = status;
-  CU_TRY(cudaMemsetAsync(status, 0, 4 * sizeof(int), st));
+  gp.status = status;           // zero in the library image; set by a kernel that gave up a wait, read and
+                                // cleared by xmc_noalloc_check
   if (f8) xmc::gradx_kernel<true><<<tiles * n_splits, xmc::kGxThreads, xmc::kGxSmemBytes, st>>>(map_a, map_b, gp);
   else xmc::gradx_kernel<false><<<tiles * n_splits, xmc::kGxThreads, xmc::kGxSmemBytes, st>>>(map_a, map_b, gp);
   CU_TRY(cudaGetLastError());
@@ -1011,6 +1022,23 @@ int xmc_large_k_matmul_noalloc(int32_t device, const void* a_bf16, const void* b
   const int blocks = (int)std::min<long long>((total + 255) / 256, (long long)sm_count * 8);
   xmc::reduce_gradx_kernel<<<blocks, 256, 0, st>>>(scratch, n_splits, m, m, n, 1.0f, c_f32, nullptr);
   CU_TRY(cudaGetLastError());
+  return XMC_OK;
+}
+
+int xmc_noalloc_check(int32_t device, void* stream) {
+  if (device < 0 || device >= kNoAllocMaxDevices) return fail(XMC_ERR_INVALID, "device %d out of range", device);
+  float* scratch = g_noalloc_ptr[device].load(std::memory_order_acquire);
+  if (scratch == nullptr) return XMC_OK;                 // no allocation-free call has run on this device yet
+  DeviceGuard guard(device);
+  cudaStream_t st = (cudaStream_t)stream;
+  CU_TRY(cudaStreamSynchronize(st));
+  int host[4] = {0, 0, 0, 0};                            // a stack array: this call allocates nothing either
+  int* status = reinterpret_cast<int*>(scratch + kNoAllocFloats);
+  CU_TRY(cudaMemcpy(host, status, sizeof(host), cudaMemcpyDeviceToHost));
+  if (host[0] != xmc::DEV_OK) {
+    CU_TRY(cudaMemset(status, 0, sizeof(host)));
+    return fail(XMC_ERR_DEVICE_FLAG, "allocation-free contraction: device status %d (block %d, site %d)", host[0], host[1], host[2]);
+  }
   return XMC_OK;
 }
 
@@ -1026,7 +1054,11 @@ int xmc_test_sigmoid(int32_t device, const void* in_bf16, void* out_bf16, int32_
 int xmc_test_gemm(int32_t device, int32_t layout, int32_t dtype, int32_t M, int32_t N, int32_t K,
                   const void* A, const void* B, float* D, void* stream) {
   if (A == nullptr || B == nullptr || D == nullptr || M <= 0 || N <= 0 || K <= 0) return fail(XMC_ERR_INVALID, "bad argument");
-  if (layout < 0 || layout > 3) return fail(XMC_ERR_INVALID, "layout must be 0..3");
+  const bool inject = (layout & 8) != 0;
+  layout &= ~8;
+  if (layout < 0 || layout > 3) return fail(XMC_ERR_INVALID, "layout must be 0..3 (| 8)");
+  if (inject && ((layout & 1) != 0 || K < 2 * (dtype == XMC_DT_E4M3 ? 128 : 64)))
+    return fail(XMC_ERR_INVALID, "the wait-limit test takes K-major operands with at least two k-steps");
   if ((layout & 1) == 1 && dtype != XMC_DT_BF16) return fail(XMC_ERR_INVALID, "MN-major test takes bf16");
   if (dtype != XMC_DT_BF16 && dtype != XMC_DT_E4M3) return fail(XMC_ERR_INVALID, "dtype");
   DeviceGuard guard(device);
@@ -1045,6 +1077,8 @@ int xmc_test_gemm(int32_t device, int32_t layout, int32_t dtype, int32_t M, int3
   p.n_ntiles = cdiv(N, 256);
   p.D = D;
   p.checksum_only = (layout & 2) ? 1 : 0;
+  p.test_wait_limit = inject ? 2000000ll : 0;      // ~1 ms
+  p.test_skip_tile = inject ? 0 : -1;
   layout &= 1;
   p.m_rows = 128;
   p.n_mtiles = cdiv(M, p.m_rows);

@@ -46,6 +46,8 @@ struct FwdPolicy {
   static constexpr bool kCTile = false;
   static constexpr int kCBufs = 1;
   static constexpr bool kBitmap = true;
+  __device__ static long long wait_limit(const Params&) { return kWaitLimitCycles; }
+  __device__ static bool skip_load(const Params&, int, int) { return false; }
   struct EpilogueState {
     float loss;
     int has_pos;
@@ -209,6 +211,8 @@ struct UpdPolicy {
   static constexpr bool kCTile = W8;
   static constexpr int kCBufs = 2;
   static constexpr bool kBitmap = false;
+  __device__ static long long wait_limit(const Params&) { return kWaitLimitCycles; }
+  __device__ static bool skip_load(const Params&, int, int) { return false; }
   static constexpr int kStages = W8 ? 3 : 4;
   __device__ static int c_col(const Job& j) { return j.b0; }
   __device__ static int c_row(const Job& j) { return j.a0; }
@@ -504,6 +508,8 @@ struct LogitsPolicy {
   static constexpr bool kCTile = false;
   static constexpr int kCBufs = 1;
   static constexpr bool kBitmap = false;
+  __device__ static long long wait_limit(const Params&) { return kWaitLimitCycles; }
+  __device__ static bool skip_load(const Params&, int, int) { return false; }
   using EpilogueState = NoState;
   __device__ static int num_tiles(const Params& p) { return p.n_mtiles * p.n_ntiles; }
   __device__ static void job(const Params& p, int tile, Job& j) {
@@ -610,6 +616,8 @@ struct TopkPolicy {
   static constexpr bool kCTile = false;
   static constexpr int kCBufs = 1;
   static constexpr bool kBitmap = false;
+  __device__ static long long wait_limit(const Params&) { return kWaitLimitCycles; }
+  __device__ static bool skip_load(const Params&, int, int) { return false; }
   struct EpilogueState {
     float thr;             // own threshold
     float g;               // published threshold of the row (refreshed per tile)
@@ -828,6 +836,8 @@ struct PlainParams {
   int k_steps;
   float* D;                // [M x N]
   int checksum_only;       // 1: do not store D (times the main loop without the output traffic)
+  long long test_wait_limit;   // > 0: every wait of the kernel gives up after this many cycles
+  int test_skip_tile;      // the producer leaves out the second k-step of this tile (-1: none)
   int* status;
 };
 
@@ -843,6 +853,9 @@ struct PlainPolicy {
   static constexpr bool kCTile = false;
   static constexpr int kCBufs = 1;
   static constexpr bool kBitmap = false;
+  // failure-injection of the self-test: a shortened wait limit and one operand load left out
+  __device__ static long long wait_limit(const Params& p) { return p.test_wait_limit > 0 ? p.test_wait_limit : kWaitLimitCycles; }
+  __device__ static bool skip_load(const Params& p, int tile, int k) { return tile == p.test_skip_tile && k == 1; }
   using EpilogueState = NoState;
   __device__ static int num_tiles(const Params& p) { return p.n_mtiles * p.n_ntiles; }
   __device__ static void job(const Params& p, int tile, Job& j) {

@@ -62,6 +62,7 @@ class StepStager:
         self._stream = torch.cuda.Stream(self.device) if self.cuda else None
         self._ready = [torch.cuda.Event() for _ in range(depth)] if self.cuda else None
         self._consumed = [None] * depth
+        self._used = [False] * depth
         self._nnz = [0] * depth
         self._rows = [0] * depth
         self._put = 0
@@ -76,6 +77,11 @@ class StepStager:
             raise ValueError(f"{n} label pairs exceed the staging capacity {self.capacity}")
         if labels.dtype != torch.int32 or (n and tuple(labels.shape[1:]) != (2,)):
             raise ValueError("labels must be int32 [nnz, 2]")
+        if self.cuda and self._used[s]:
+            # the pinned slot is about to be rewritten by the host: the copy that last read it (queued on
+            # the side stream behind the step two puts ago) must have run, or that step would see these data
+            self._ready[s].synchronize()
+        self._used[s] = True
         self._nnz[s] = n
         self._h_lab[s][:n].copy_(labels.reshape(n, 2))
         if embed is not None:

@@ -74,9 +74,12 @@ class LabelShardedXMC:
 
     def __init__(self, engine, *, dim: int, local_batch: int, num_rows: int, group=None,
                  label_capacity: Optional[int] = None, device=None, base_seed: int = 0,
-                 rounding: str = "sr"):
+                 rounding: str = "sr", time_comm: bool = False):
         self.engine = engine
         self.group = group
+        self.num_rows = num_rows
+        self.time_comm = time_comm          # record CUDA events around the collectives (bench bookkeeping)
+        self._comm_events = []
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.dim, self.local_batch = dim, local_batch
@@ -98,9 +101,40 @@ class LabelShardedXMC:
         lab = pad_labels(labels_local, self.capacity, self.rank * self.local_batch, self.device)
         if self.world == 1:
             return x, lab
-        dist.all_gather_into_tensor(self._xg, x, group=self.group)
-        dist.all_gather_into_tensor(self._lg, lab, group=self.group)
+        with self._comm():
+            dist.all_gather_into_tensor(self._xg, x, group=self.group)
+            dist.all_gather_into_tensor(self._lg, lab, group=self.group)
         return self._xg, self._lg
+
+    # --- collective timing -------------------------------------------------------------------
+    class _Span:
+        def __init__(self, owner):
+            self.o = owner
+
+        def __enter__(self):
+            o = self.o
+            if o.time_comm and o.device.type == "cuda":
+                self.e0 = torch.cuda.Event(enable_timing=True)
+                self.e1 = torch.cuda.Event(enable_timing=True)
+                self.e0.record(torch.cuda.current_stream(o.device))
+
+        def __exit__(self, *a):
+            o = self.o
+            if o.time_comm and o.device.type == "cuda":
+                self.e1.record(torch.cuda.current_stream(o.device))
+                o._comm_events.append((self.e0, self.e1))
+
+    def _comm(self):
+        return LabelShardedXMC._Span(self)
+
+    def comm_ms(self) -> float:
+        """Device milliseconds spent inside the collectives since the last call (``time_comm`` only)."""
+        if not self._comm_events:
+            return 0.0
+        self._comm_events[-1][1].synchronize()
+        ms = sum(a.elapsed_time(b) for a, b in self._comm_events)
+        self._comm_events = []
+        return ms
 
     @torch.no_grad()
     def xfc_topk(self, embed_local, k: int, num_labels: int):
@@ -124,8 +158,9 @@ class LabelShardedXMC:
         if self.world > 1:
             all_v = torch.empty(self.world * B, k, dtype=vals.dtype, device=self.device)
             all_i = torch.empty(self.world * B, k, dtype=idx.dtype, device=self.device)
-            dist.all_gather_into_tensor(all_v, vals.contiguous(), group=self.group)
-            dist.all_gather_into_tensor(all_i, idx.contiguous(), group=self.group)
+            with self._comm():
+                dist.all_gather_into_tensor(all_v, vals.contiguous(), group=self.group)
+                dist.all_gather_into_tensor(all_i, idx.contiguous(), group=self.group)
             cand_v = all_v.view(self.world, B, k).permute(1, 0, 2).reshape(B, self.world * k)
             cand_i = all_i.view(self.world, B, k).permute(1, 0, 2).reshape(B, self.world * k)
             # shards are in ascending label order, so a stable descending sort keeps the lower id on ties
@@ -141,7 +176,83 @@ class LabelShardedXMC:
         if self.world == 1:
             self._gl = self._g32
         else:
-            dist.reduce_scatter_tensor(self._gl, self._g32, op=dist.ReduceOp.SUM, group=self.group)
+            with self._comm():
+                dist.reduce_scatter_tensor(self._gl, self._g32, op=dist.ReduceOp.SUM, group=self.group)
         self.grad_input = self._gl.to(torch.bfloat16)
         self.iteration += 1
         return 0
+
+    # --- checkpoint (runner.py:242-251 saves ``xmc_weight: model.xfc.xfc_weight``) ---------------
+    def state_dict(self):
+        """This rank's part of the layer: its weight chunks (CPU copies), the shard map that says which
+        label rows they are, and the position of the stochastic-rounding stream.  Every rank saves its
+        own; ``load_state_dict`` checks that the map matches the layer it is loaded into."""
+        lo, hi = self.bounds[self.rank]
+        return {"shard_map": {"world": self.world, "rank": self.rank, "num_rows": self.num_rows,
+                              "bounds": [list(b) for b in self.bounds], "rows": [lo, hi]},
+                "weights": [w.detach().cpu().clone() for w in self.engine.weights],
+                "base_seed": self.base_seed, "iteration": self.iteration, "rounding": self.rounding,
+                "w_scale": getattr(self.engine, "w_scale", 1.0)}
+
+    def load_state_dict(self, sd):
+        m = sd["shard_map"]
+        if (m["world"], m["rank"], m["num_rows"]) != (self.world, self.rank, self.num_rows) or \
+                [list(b) for b in self.bounds] != [list(b) for b in m["bounds"]]:
+            raise ValueError(f"checkpoint shard map {m} does not match this layer "
+                             f"(world {self.world}, rank {self.rank}, rows {self.num_rows})")
+        if len(sd["weights"]) != len(self.engine.weights):
+            raise ValueError("checkpoint has a different number of weight chunks")
+        for dst, src in zip(self.engine.weights, sd["weights"]):
+            if dst.shape != src.shape or dst.dtype != src.dtype:
+                raise ValueError(f"weight chunk mismatch: {tuple(src.shape)} {src.dtype} vs {tuple(dst.shape)} {dst.dtype}")
+            dst.copy_(src)
+        self.base_seed, self.iteration = int(sd["base_seed"]), int(sd["iteration"])
+        self.rounding = sd.get("rounding", self.rounding)
+
+    def _local_rows(self) -> torch.Tensor:
+        return torch.cat([w.detach() for w in self.engine.weights], 0)
+
+    @torch.no_grad()
+    def export_reference_layout(self, num_labels: int, num_chunks: int):
+        """The whole layer in the reference's layout, on every rank: the list of ``num_chunks`` e4m3
+        tensors ``[L_i, d]`` that ``Fp8XMCBCEChunkedLayer.xfc_weight`` holds (padding rule of
+        chunked_fp8xmc_clf.py:26-28; rows this layer does not have are zero).  For bf16 weights pass
+        ``num_chunks=0`` to get the dense ``[num_labels, d]`` tensor of ``XMCBCECHUNKEDLayer``."""
+        mine = self._local_rows()
+        per = max(hi - lo for lo, hi in self.bounds)
+        raw = mine.view(torch.uint8) if mine.element_size() == 1 else mine.view(torch.int16)
+        pad = torch.zeros(per, raw.shape[1], dtype=raw.dtype, device=raw.device)
+        pad[:raw.shape[0]] = raw
+        if self.world > 1:
+            allr = torch.empty(self.world * per, raw.shape[1], dtype=raw.dtype, device=raw.device)
+            dist.all_gather_into_tensor(allr, pad, group=self.group)
+            parts = [allr[r * per:r * per + (hi - lo)] for r, (lo, hi) in enumerate(self.bounds)]
+            rows = torch.cat(parts, 0)
+        else:
+            rows = pad[:raw.shape[0]]
+        rows = rows.view(mine.dtype)
+        if num_chunks <= 0:
+            return rows[:num_labels].contiguous()
+        lp = num_labels + 16 * num_chunks - num_labels % (16 * num_chunks)
+        li = lp // num_chunks
+        full = torch.zeros(lp, rows.shape[1], dtype=torch.uint8, device=rows.device).view(mine.dtype) \
+            if mine.element_size() == 1 else torch.zeros(lp, rows.shape[1], dtype=mine.dtype, device=rows.device)
+        n = min(lp, rows.shape[0])
+        full[:n] = rows[:n]
+        return [full[i * li:(i + 1) * li].contiguous() for i in range(num_chunks)]
+
+    @torch.no_grad()
+    def import_reference_layout(self, chunks):
+        """Inverse of ``export_reference_layout``: every rank takes its label rows out of the reference's
+        chunk list (or dense tensor)."""
+        rows = torch.cat(list(chunks), 0) if isinstance(chunks, (list, tuple, torch.nn.ParameterList)) else chunks
+        lo, hi = self.bounds[self.rank]
+        src = rows[lo:min(hi, rows.shape[0])]
+        off = 0
+        for w in self.engine.weights:
+            n = max(0, min(w.shape[0], src.shape[0] - off))
+            if n:
+                w[:n].copy_(src[off:off + n])
+            if n < w.shape[0]:
+                w[n:].zero_() if w.element_size() != 1 else w.view(torch.uint8)[n:].zero_()
+            off += w.shape[0]

@@ -40,7 +40,8 @@ class XMCBCECHUNKEDLayer(nn.Module):
         # the reference's bf16 path always rounds stochastically (stochastic_rounding_kernel.py:82-89)
         self.rounding = cfg_get(cfg, 'training.xmc.rounding', 'sr')
         self.base_seed = draw_base_seed()
-        self._handle = XmcHandle(self.device, d, cfg.data.batch_size, 'bf16',
+        self.max_batch = max(int(cfg.data.batch_size), int(cfg_get(cfg, 'data.test_batch_size', 0) or 0))
+        self._handle = XmcHandle(self.device, d, self.max_batch, 'bf16',
                                  label_offset=cfg_get(cfg, 'model.xmc.label_offset', 0),
                                  sched_labels=cfg_get(cfg, 'model.xmc.sched_labels', 0))
 

@@ -39,12 +39,14 @@ class Fp8XMCBCEChunkedLayer(nn.Module):
         self.block_size = 16
         self.loss = torch.tensor(0.0, device=self.device)
         self._loss_dev = torch.zeros(1, dtype=torch.float64, device=self.device)
+        # inference batches may be larger than training batches (src/config.py keeps the two apart)
+        self.max_batch = max(int(cfg.data.batch_size), int(cfg_get(cfg, 'data.test_batch_size', 0) or 0))
         self._grad_buf = torch.zeros(cfg.data.batch_size, d, dtype=torch.bfloat16, device=self.device)
         self.grad_input = self._grad_buf
         self.iteration = 0
         self.rounding = cfg_get(cfg, 'training.xmc.rounding', 'sr')
         self.base_seed = draw_base_seed()
-        self._handle = XmcHandle(self.device, d, cfg.data.batch_size,
+        self._handle = XmcHandle(self.device, d, self.max_batch,
                                  'simfp8' if self.fake_fp8_matmul else 'fp8',
                                  label_offset=cfg_get(cfg, 'model.xmc.label_offset', 0),
                                  sched_labels=cfg_get(cfg, 'model.xmc.sched_labels', 0),
@@ -101,7 +103,3 @@ class Fp8XMCBCEChunkedLayer(nn.Module):
         self.base_seed = int(state.get("base_seed", self.base_seed))
         self.iteration = int(state.get("iteration", self.iteration))
         self.rounding = state.get("rounding", self.rounding)
-
-    def filter_non_local_inds(self, rows, cols, start, end):
-        mask = (cols >= start) & (cols < end)                                          # :124-126
-        return rows[mask], cols[mask] - start

@@ -73,7 +73,14 @@ typedef struct {
   int32_t reserved;
 } xmc_config;
 
-/* Create a handle and its workspaces on cfg->device (cudaMalloc; freed by xmc_destroy). */
+/*
+ * Create a handle and its workspaces on cfg->device (cudaMalloc; freed by xmc_destroy).
+ * Side effect on the CUDA context: unless XMC_NO_L2_PERSIST is set in the environment, the call raises
+ * cudaLimitPersistingL2CacheSize to the size of the grad_X partial sums (<= 38 MB on a B200); that much
+ * L2 is then reserved for persisting lines process-wide.  xmc_step installs an access-policy window over
+ * that private buffer on the caller's stream for the duration of its launches and removes it before it
+ * returns; xmc_destroy resets the persisting lines.
+ */
 int xmc_create(const xmc_config* cfg, xmc_handle** out);
 int xmc_destroy(xmc_handle* h);
 
@@ -165,15 +172,26 @@ const char* xmc_version(void);
  * in a cudaMalloc'd workspace live in an 8 MiB array built into the library image instead (every GPU
  * that loads the library holds it until the process exits).
  *   - limit: m * n <= 2 097 152 (8 MiB of fp32); larger shapes are rejected with XMC_ERR_INVALID --
- *     use the handle-based API for those.  m and n must be multiples of 64; c 16-byte aligned.
- *   - the first call on a device looks up the array's device address and sets kernel attributes; make
- *     that first call outside any stream capture.
+ *     use the handle-based API for those.  m and n must be multiples of 64; a, b and c 16-byte aligned.
+ *   - the first call on a device looks up the array's device address and sets kernel attributes, which
+ *     also makes the driver load the library's code and the 8 MiB array onto that device: make that
+ *     first call outside any stream capture and before a pool takes all of the device's memory.
  *   - all calls share the one array and it keeps the last call's contents: two calls whose kernels
- *     overlap on the GPU (different streams) race.  Serialise them on one stream.
+ *     overlap on the GPU (different streams) race.  Serialise them on one stream.  The first call per
+ *     device may be made from several host threads at once (they agree on the address).
  *   - asynchronous on `stream`; neither cudaMalloc/cudaFree nor any allocating routine is called.
+ *   - a kernel that gives up a bounded wait leaves a status word in the array; the call itself has long
+ *     returned XMC_OK by then.  xmc_noalloc_check reads it.
  */
 int xmc_large_k_matmul_noalloc(int32_t device, const void* a_bf16, const void* b, int32_t b_dtype,
                                int32_t k, int32_t m, int32_t n, float* c_f32, void* stream);
+
+/*
+ * Companion of xmc_large_k_matmul_noalloc, equally allocation-free and without a counterpart in the
+ * reference: synchronise `stream`, then read and clear the status word the allocation-free kernels
+ * report to (XMC_OK, or XMC_ERR_DEVICE_FLAG with block and wait site in xmc_last_error).
+ */
+int xmc_noalloc_check(int32_t device, void* stream);
 
 /*
  * Test hook (not used by the layer classes): D[M x N] fp32 = A * B^T on the library's GEMM
@@ -181,6 +199,10 @@ int xmc_large_k_matmul_noalloc(int32_t device, const void* a_bf16, const void* b
  *   layout 0: A [M x K], B [N x K] both K-major (row-major as written), dtype XMC_DT_BF16 or XMC_DT_E4M3
  *   layout 1: A given as [K x M], B as [K x N] row-major (both "MN-major"), dtype XMC_DT_BF16
  *   layout | 2: same contraction, but D is not stored (times the main loop alone)
+ *   layout | 8 (with layout 0): exercises the kernels' failure handling without faulting anything: the
+ *               producer leaves out one operand load of tile 0 and every wait of the launch is limited to
+ *               about a millisecond, so the wait for that load gives up, the CTA unwinds, and the call
+ *               returns XMC_ERR_DEVICE_FLAG naming the wait; D is then undefined, the context stays usable
  * M, N, K arbitrary positive (rows 16-byte aligned: inner extents multiples of 8 (bf16) / 16 (e4m3)).
  */
 int xmc_test_gemm(int32_t device, int32_t layout, int32_t dtype, int32_t M, int32_t N, int32_t K,

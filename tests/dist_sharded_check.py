@@ -17,11 +17,9 @@ from elmo_b200.sharded import CudaShardEngine, LabelShardedXMC, shard_bounds  # 
 from oracle import xmc_oracle as O  # noqa: E402
 
 
-def main():
-    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
-    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank)))
-    torch.cuda.set_device(dev)
-    dist.init_process_group("nccl", device_id=dev)
+def run_check(dev, rank, world):
+    """Sharded CUDA layer vs the CPU oracle on the unsharded problem, inside an initialised process group.
+    Returns {"w_bit_exact", "grad_x_rel", "topk_value_err", "ok"} reduced over all ranks (worst case)."""
     L, d, b_loc, k = 4000 - 16, 128, 48, 7
     g = torch.Generator().manual_seed(0)
     w = (torch.randn(L, d, generator=g) * 0.25).to(torch.float8_e4m3fn)
@@ -47,21 +45,33 @@ def main():
     chunks = [w]
     for it in range(2):
         chunks, gx, _ = O.fp8_chunked_step(chunks, x, lab, 0.4, rounding="sr", seed=77, step=it)
-    same = (mine[0].cpu().view(torch.uint8) == chunks[0][lo:hi].view(torch.uint8)).float().mean()
+    same = float((mine[0].cpu().view(torch.uint8) == chunks[0][lo:hi].view(torch.uint8)).float().mean()) if hi > lo else 1.0
     gwant = gx[rank * b_loc:(rank + 1) * b_loc]
     gerr = float((layer.grad_input.float().cpu() - gwant).abs().max() / gwant.abs().max())
     wv, wi = O.topk_logits([chunks[0][:L - 5]], xs[rank], k)
     z = O.forward_logits([chunks[0]], xs[rank], num_labels=L - 5).float()
     ulp = float(z.abs().max()) * 2.0 ** -7
     verr = float((tv.cpu() - wv).abs().max())
-    ok = bool(same >= 0.999) and gerr < 1e-2 and verr <= ulp and int(ti.min()) >= 0 and int(ti.max()) < L - 5
-    flag = torch.tensor([1 if ok else 0], device=dev)
-    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-    print(f"rank {rank}: W' bit-exact {float(same):.5f}, grad_X rel err {gerr:.2e}, top-k value err {verr:.2e} "
-          f"-> {'ok' if ok else 'FAIL'}", flush=True)
+    ok = same >= 0.999 and gerr < 1e-2 and verr <= ulp and int(ti.min()) >= 0 and int(ti.max()) < L - 5
+    red = torch.tensor([same, -gerr, -verr, 1.0 if ok else 0.0], device=dev, dtype=torch.float64)
+    dist.all_reduce(red, op=dist.ReduceOp.MIN)
+    eng.handle.close()
+    return {"w_bit_exact": float(red[0]), "grad_x_rel": float(-red[1]), "topk_value_err": float(-red[2]),
+            "ok": bool(red[3] > 0.5), "ranks": world,
+            "case": f"{L} labels x {d}, batch {b_loc} per rank, 2 SR steps + top-{k}, vs the CPU oracle unsharded"}
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank)))
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    res = run_check(dev, rank, world)
+    print(f"rank {rank}: W' bit-exact {res['w_bit_exact']:.5f}, grad_X rel err {res['grad_x_rel']:.2e}, "
+          f"top-k value err {res['topk_value_err']:.2e} -> {'ok' if res['ok'] else 'FAIL'}", flush=True)
     dist.barrier()
     dist.destroy_process_group()
-    sys.exit(0 if int(flag.item()) == 1 else 1)
+    sys.exit(0 if res["ok"] else 1)
 
 
 if __name__ == "__main__":

@@ -39,3 +39,20 @@ def test_mnmajor_bf16(m, n, k):
     d = test_gemm(a, b, 1)
     ref = a.float().t() @ b.float()
     assert torch.allclose(d, ref, rtol=1e-4, atol=2e-3), float((d - ref).abs().max())
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_context_survives():
+    """Failure handling without a fault: the self-test leaves out one operand load and shortens the wait
+    limit to about a millisecond.  The wait for the missing load gives up, the CTA unwinds (tensor memory
+    freed), the call reports XMC_ERR_DEVICE_FLAG with the wait's site, and the next call works."""
+    from elmo_b200._lib import XmcError
+    from elmo_b200.handle import test_gemm
+    g = torch.Generator().manual_seed(5)
+    a = _rand((256, 512), torch.bfloat16, g); b = _rand((256, 512), torch.bfloat16, g)
+    # whichever wait of the chain behind the missing load started first reports: the MMA issuer's wait for
+    # the operand stage (sites 300-303) or the epilogue's wait for the accumulator (400, 401)
+    with pytest.raises(XmcError, match=r"device status 1 .*site (30[0-3]|40[01])") as exc:
+        test_gemm(a, b, 8)
+    assert exc.value.code == 4                                   # XMC_ERR_DEVICE_FLAG
+    d = test_gemm(a, b, 0)                                       # the context is intact
+    assert torch.allclose(d, a.float() @ b.float().t(), rtol=1e-4, atol=1e-3)

@@ -55,7 +55,27 @@ def _worker(rank, port, out):
         for it in range(2):
             layer.xfc_forward_backward(xs[rank], labs[rank], [0.5])
         tv, ti = layer.xfc_topk(xs[rank], 4, L - 7)
-        out[rank] = (mine[0].view(torch.uint8).clone(), layer.grad_input.float().clone(), tv.clone(), ti.clone())
+        # checkpoint: per-rank state with its shard map, and the gathered reference layout (3 chunks)
+        sd = layer.state_dict()
+        ref_chunks = layer.export_reference_layout(L - 7, 3)
+        twin_w = [torch.zeros_like(mine[0])]
+        twin = LabelShardedXMC(OracleEngine(twin_w, lo), dim=D, local_batch=B_LOC, num_rows=L,
+                               label_capacity=16, base_seed=0, rounding="rn")
+        twin.load_state_dict(sd)
+        ok_sd = torch.equal(twin_w[0].view(torch.uint8), mine[0].view(torch.uint8)) and twin.iteration == 2 \
+            and twin.base_seed == 9 and twin.rounding == "sr"
+        twin_w[0].view(torch.uint8).zero_()
+        twin.import_reference_layout(ref_chunks)
+        n_keep = max(0, min(hi, sum(c.shape[0] for c in ref_chunks)) - lo)
+        ok_imp = torch.equal(twin_w[0].view(torch.uint8)[:n_keep], mine[0].view(torch.uint8)[:n_keep])
+        bad_map = dict(sd, shard_map=dict(sd["shard_map"], world=3))
+        try:
+            twin.load_state_dict(bad_map)
+            ok_rej = False
+        except ValueError:
+            ok_rej = True
+        out[rank] = (mine[0].view(torch.uint8).clone(), layer.grad_input.float().clone(), tv.clone(), ti.clone(),
+                     [c.view(torch.uint8).clone() for c in ref_chunks], bool(ok_sd and ok_imp and ok_rej))
     finally:
         dist.destroy_process_group()
 
@@ -74,8 +94,15 @@ def test_two_rank_sharded_step_equals_unsharded():
         chunks, gx, _ = O.fp8_chunked_step(chunks, x, lab, 0.5, rounding="sr", seed=9, step=it)
     full = chunks[0].view(torch.uint8)
     for r, (lo, hi) in enumerate(shard_bounds(L, WORLD)):
-        w_r, g_r, tv, ti = out[r]
+        w_r, g_r, tv, ti, ref_chunks, ok_ckpt = out[r]
         assert torch.equal(w_r, full[lo:hi])
+        assert ok_ckpt
+        # the exported list has the reference's padded geometry and holds the unsharded weights
+        lp, li = O.fp8_padded_labels(L - 7, 3)
+        assert len(ref_chunks) == 3 and all(c.shape == (li, D) for c in ref_chunks)
+        cat = torch.cat(ref_chunks)
+        n = min(lp, L)
+        assert torch.equal(cat[:n], full[:n]) and int(cat[n:].sum()) == 0
         want = gx[r * B_LOC:(r + 1) * B_LOC].to(torch.bfloat16).float()
         assert torch.allclose(g_r, want, rtol=2e-2, atol=1e-6)
         # sharded top-k (after the two steps) == top-k of the unsharded updated weights
