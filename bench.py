@@ -225,7 +225,7 @@ def run_reference(args, wl, rank, world):
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "e4m3/bf16 storage, fp32 arithmetic on CPU",
+        "scaling": args.scaling, "vs_baseline": None, "dtype": "e4m3/bf16 storage, fp32 arithmetic on CPU",
         "data": "synthetic", "config": workload_config(wl, world), "cpu_baseline": cpu,
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
@@ -405,7 +405,7 @@ def run_ours(args, wl, rank, local_rank, world):
     out = {
         "metric": METRIC, "value": B * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None,
+        "scaling": args.scaling, "vs_baseline": None,
         "dtype": ("bf16 weights; all contractions bf16 x bf16, fp32 accumulate" if wl.mode == "bf16" else
                   "e4m3 weights; forward e4m3 x e4m3, backward bf16 x bf16, fp32 accumulate" if wl.mode == "fp8" else
                   "e4m3 weights up-converted to bf16; all contractions bf16 x bf16, fp32 accumulate"),
@@ -434,41 +434,64 @@ def run_ours(args, wl, rank, local_rank, world):
     print(json.dumps(out))
 
 
-def run_topk(args, wl):
-    """``--pass topk``: the fused logits + top-k inference pass over the same layer (single GPU, one
-    line of its own; the default run never comes here)."""
+def run_topk(args, wl, rank, local_rank, world):
+    """``--pass topk``: the fused logits + top-k inference pass (a line of its own; the default run never
+    comes here).  One GPU: through ``Fp8XMCBCEChunkedLayer.xfc_topk``.  N GPUs: label shards, the batch
+    of wl.batch rows per rank all-gathered, per-shard top-k candidates all-gathered and merged."""
+    import torch.distributed as dist
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (sm_100a); there is no CPU fallback"
-    device = torch.device("cuda", 0)
+    device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
-    from elmo_b200.xmc_classifiers import Fp8XMCBCEChunkedLayer
-    layer = Fp8XMCBCEChunkedLayer(layer_cfg(wl, device, wl.batch, sched=args.sched))
-    fill_weights([p.data for p in layer.xfc_weight], wl.dim, seed=0)
-    gen = torch.Generator().manual_seed(5)
-    xs = [synth.make_embeddings(wl.batch, wl.dim, gen).to(device) for _ in range(4)]
     k = args.topk
+    B = wl.batch * world
+    gen = torch.Generator().manual_seed(5 + rank)
+    xs = [synth.make_embeddings(wl.batch, wl.dim, gen).to(device) for _ in range(4)]
+    sharded = None
+    if world == 1:
+        from elmo_b200.xmc_classifiers import Fp8XMCBCEChunkedLayer
+        layer = Fp8XMCBCEChunkedLayer(layer_cfg(wl, device, wl.batch, sched=args.sched))
+        fill_weights([p.data for p in layer.xfc_weight], wl.dim, seed=0)
+        handle = layer._handle
+        call = lambda x: layer.xfc_topk(x, k)
+    else:
+        dist.init_process_group("nccl", device_id=device)
+        from elmo_b200.sharded import CudaShardEngine, LabelShardedXMC, shard_bounds
+        n_rows = padded_rows(wl, world)
+        lo, hi = shard_bounds(n_rows, world)[rank]
+        w = torch.empty(hi - lo, wl.dim, dtype=torch.float8_e4m3fn, device=device)
+        fill_weights([w], wl.dim, seed=rank)
+        engine = CudaShardEngine(device, wl.dim, B, wl.mode, lo, [w], sched_labels=args.sched)
+        sharded = LabelShardedXMC(engine, dim=wl.dim, local_batch=wl.batch, num_rows=n_rows, device=device,
+                                  time_comm=True)
+        handle = engine.handle
+        call = lambda x: sharded.xfc_topk(x, k, wl.num_labels)
     for i in range(max(3, args.warmup)):
-        layer.xfc_topk(xs[i % 4], k)
-    torch.cuda.synchronize(device)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
-        vals, idx = layer.xfc_topk(xs[i % 4], k)
-    e1.record()
-    torch.cuda.synchronize(device)
-    layer._handle.check()
-    ms = e0.elapsed_time(e1) / args.steps
-    flops = 2.0 * wl.batch * wl.num_labels * wl.dim
+        call(xs[i % 4])
+    if sharded is not None:
+        sharded.comm_ms()
+    ms = timed_block(lambda i: call(xs[i % 4]), 0, args.steps, world, device) / args.steps
+    comm = sharded.comm_ms() / args.steps if sharded is not None else None
+    handle.check()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    flops = 2.0 * B * wl.num_labels * wl.dim
     pk = peaks()
-    print(json.dumps({
-        "metric": "xmc_layer_topk_samples_per_sec", "value": wl.batch / (ms * 1e-3), "unit": UNIT, "n_gpus": 1,
+    out = {
+        "metric": "xmc_layer_topk_samples_per_sec", "value": B / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
         "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True,
         "dtype": "e4m3 x e4m3, fp32 accumulate, bf16 logits", "data": "synthetic",
-        "config": {"workload": f"{wl.name}: top-{k} of W[{wl.num_labels}x{wl.dim}] e4m3 for X[{wl.batch}x{wl.dim}] bf16",
-                   "l2": "weights larger than L2"},
-        "roofline": {"bound": "tensor", "kernel": "top-k", "achieved": flops / (ms * 1e-3) / 1e12,
+        "config": {"workload": f"{wl.name}: top-{k} of W[{wl.num_labels}x{wl.dim}] e4m3 for X[{B}x{wl.dim}] bf16",
+                   "parallelism": f"label-shard x{world}", "l2": "weights larger than L2"},
+        "roofline": {"bound": "tensor", "kernel": "top-k", "achieved": flops / world / (ms * 1e-3) / 1e12,
                      "peak": pk["bf16_sustained"] * 2.0, "unit": "TFLOP/s",
-                     "frac": flops / (ms * 1e-3) / 1e12 / (pk["bf16_sustained"] * 2.0), "traffic": None,
-                     "peak_source": pk["source"] + " bf16 sustained x2 (no measured fp8 figure)"}}))
+                     "frac": flops / world / (ms * 1e-3) / 1e12 / (pk["bf16_sustained"] * 2.0), "traffic": None,
+                     "peak_source": pk["source"] + " bf16 sustained x2 (no measured fp8 figure)"}}
+    if comm is not None:
+        out["comm_ms_per_step"] = comm
+    print(json.dumps(out))
 
 
 def main():
@@ -486,6 +509,8 @@ def main():
     ap.add_argument("--pass", dest="which", default="train", choices=["train", "topk"],
                     help="train = the layer's train step (default); topk = the fused top-k inference pass")
     ap.add_argument("--topk", type=int, default=5)
+    ap.add_argument("--global-batch", type=int, default=0,
+                    help="fix the GLOBAL batch (per-rank batch = this / N): strong scaling instead of the default weak scaling")
     args = ap.parse_args()
     rank, local_rank, world = env_int("RANK", 0), env_int("LOCAL_RANK", 0), env_int("WORLD_SIZE", 1)
     wl = synth.WORKLOADS[args.workload]
@@ -496,13 +521,16 @@ def main():
     if args.rounding:
         import dataclasses
         wl = dataclasses.replace(wl, rounding=args.rounding)
+    args.scaling = "weak"
+    if args.global_batch:
+        import dataclasses
+        assert args.global_batch % (16 * world) == 0, "global batch must split into multiples of 16 rows per rank"
+        wl = dataclasses.replace(wl, batch=args.global_batch // world)
+        args.scaling = "strong"
     if args.impl == "reference":
         run_reference(args, wl, rank, world)
     elif args.which == "topk":
-        if world == 1:
-            run_topk(args, wl)
-        elif rank == 0:
-            print(json.dumps({"metric": "xmc_layer_topk_samples_per_sec", "unavailable": "--pass topk is a single-GPU line"}))
+        run_topk(args, wl, rank, local_rank, world)
     else:
         run_ours(args, wl, rank, local_rank, world)
 

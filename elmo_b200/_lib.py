@@ -40,6 +40,10 @@ _SIGNATURES = {
     "xmc_forward_topk": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int64,
                                    C.c_void_p, C.c_void_p, C.c_void_p]),
     "xmc_check": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "xmc_weight_stats": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_float), C.c_void_p]),
+    "xmc_rescale": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_uint64, C.c_uint64, C.c_void_p]),
+    "xmc_get_scale": (C.c_float, [C.c_void_p]),
+    "xmc_set_scale": (C.c_int, [C.c_void_p, C.c_float]),
     "xmc_workspace_bytes": (C.c_int64, [C.c_void_p]),
     "xmc_launch_count": (C.c_int64, [C.c_void_p]),
     "xmc_profile": (C.c_int, [C.c_void_p, C.c_int32, C.POINTER(C.c_double), C.POINTER(C.c_int64)]),

@@ -209,6 +209,73 @@ __global__ void e4m3_to_bf16_kernel(const uint4* __restrict__ src, uint4* __rest
   }
 }
 
+// Scale bookkeeping: one streaming pass over e4m3 weights (n16 groups of 16 bytes).
+// counts[0] zeros, [1] sub-normal magnitudes (0 < |w| < 2^-6), [2] at +-448, [3] NaN; amax_bits = largest
+// magnitude byte seen (e4m3 magnitudes order like their bytes).
+__global__ void weight_stats_kernel(const uint4* __restrict__ w, long long n16, unsigned long long* counts,
+                                    unsigned int* amax_bits) {
+  unsigned int zeros = 0, sub = 0, sat = 0, nan = 0, amax = 0;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += stride) {
+    const uint4 raw = w[i];
+    const uint32_t ws[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const unsigned int m = (ws[k] >> (8 * b)) & 0x7Fu;
+        zeros += m == 0u;
+        sub += (m != 0u) & (m < 0x08u);
+        sat += m == 0x7Eu;
+        nan += m == 0x7Fu;
+        amax = max(amax, m == 0x7Fu ? 0u : m);
+      }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    zeros += __shfl_xor_sync(0xffffffffu, zeros, o);
+    sub += __shfl_xor_sync(0xffffffffu, sub, o);
+    sat += __shfl_xor_sync(0xffffffffu, sat, o);
+    nan += __shfl_xor_sync(0xffffffffu, nan, o);
+    amax = max(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  }
+  if ((threadIdx.x & 31) == 0) {
+    if (zeros) atomicAdd(&counts[0], (unsigned long long)zeros);
+    if (sub) atomicAdd(&counts[1], (unsigned long long)sub);
+    if (sat) atomicAdd(&counts[2], (unsigned long long)sat);
+    if (nan) atomicAdd(&counts[3], (unsigned long long)nan);
+    atomicMax(amax_bits, amax);
+  }
+}
+
+// stored <- round(stored * factor) for a power-of-two factor (the per-tensor scale moves the other way).
+// Growing is exact up to saturation at +-448; shrinking rounds what falls below the grid: to nearest, or
+// stochastically with the step's Philox stream (counter = global element index / 8, as in the update).
+__global__ void rescale_e4m3_kernel(uint2* __restrict__ w, long long n8, float factor, int stochastic,
+                                    unsigned long long seed, unsigned long long step, unsigned long long elem0) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += stride) {
+    const uint2 raw = w[i];
+    const uint32_t rw[2] = {raw.x, raw.y};
+    uint4 r = make_uint4(0u, 0u, 0u, 0u);
+    if (stochastic) {
+      const unsigned long long q = (elem0 >> 3) + (unsigned long long)i;
+      r = philox4x32_10(make_uint4((uint32_t)q, (uint32_t)(q >> 32), (uint32_t)step, (uint32_t)(step >> 32)),
+                        make_uint2((uint32_t)seed, (uint32_t)(seed >> 32)));
+    }
+    const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
+    uint32_t ow[2] = {0u, 0u};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      float v = e4m3x2_to_float2((uint16_t)(rw[e >> 2] >> (8 * (e & 3)))).x * factor;
+      if (stochastic) v = sr_e4m3(v, (e & 1) ? (rr[e >> 1] >> 16) : (rr[e >> 1] & 0xFFFFu));
+      ow[e >> 2] |= ((uint32_t)float2_to_e4m3x2(v, 0.f) & 0xFFu) << (8 * (e & 3));
+    }
+    w[i] = make_uint2(ow[0], ow[1]);
+  }
+}
+
 // out[i] = bf16(sigmoid(in[i])) exactly as the forward epilogue computes it (test hook)
 __global__ void sigmoid_probe_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int n) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;

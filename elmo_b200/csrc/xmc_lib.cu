@@ -243,6 +243,7 @@ struct xmc_handle {
   double* loss_partial = nullptr;
   int64_t loss_cap = 0;
   int* status = nullptr;           // 4 ints
+  unsigned long long* stats = nullptr;   // weight statistics: 4 counters + the largest magnitude byte
   int64_t ws_bytes = 0;
   // bookkeeping for the bench: kernels launched so far, optional per-kernel-class event timing
   float* topk_val = nullptr;       // candidate lists of the fused top-k (grown on demand)
@@ -400,7 +401,7 @@ int xmc_destroy(xmc_handle* h) {
   DeviceGuard guard(h->cfg.device);
   if (h->l2_persist_bytes > 0) cudaCtxResetPersistingL2Cache();   // lines pinned for the partial sums become normal again
   void* ptrs[] = {h->x8, h->x16, h->xt, h->G, h->w16, h->partial, h->bucket_cnt, h->bucket_off,
-                  h->entries, h->loss_partial, h->status, h->topk_val, h->topk_idx, h->topk_cnt, h->topk_thr, h->topk_max, h->topk_row};
+                  h->entries, h->loss_partial, h->status, h->stats, h->topk_val, h->topk_idx, h->topk_cnt, h->topk_thr, h->topk_max, h->topk_row};
   for (void* p : ptrs)
     if (p != nullptr) cudaFree(p);
   for (cudaEvent_t e : h->ev_pool) cudaEventDestroy(e);
@@ -474,6 +475,69 @@ int xmc_bind_kahan(xmc_handle* h, void* buf, int64_t rows, int32_t dtype) {
   h->kahan = buf;
   h->kahan_rows = rows;
   h->kahan_e5m2 = dtype == XMC_DT_E5M2 ? 1 : 0;
+  return XMC_OK;
+}
+
+int xmc_weight_stats(xmc_handle* h, int64_t* counts, float* amax_stored, void* stream) {
+  if (h == nullptr || counts == nullptr || amax_stored == nullptr) return fail(XMC_ERR_INVALID, "null argument");
+  if (h->w_ptrs.empty()) return fail(XMC_ERR_STATE, "xmc_bind_weights has not been called");
+  if (h->cfg.mode == XMC_MODE_BF16) return fail(XMC_ERR_STATE, "weight statistics are defined for e4m3 weights");
+  DeviceGuard guard(h->cfg.device);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (h->stats == nullptr) {
+    if (int rc = dev_alloc(h, (void**)&h->stats, 8 * sizeof(unsigned long long), true)) return rc;
+  }
+  CU_TRY(cudaMemsetAsync(h->stats, 0, 8 * sizeof(unsigned long long), st));
+  const int d = h->cfg.dim;
+  for (size_t wc = 0; wc < h->w_ptrs.size(); ++wc) {
+    const long long n16 = (long long)h->w_rows[wc] * d / 16;
+    const int blocks = (int)std::min<long long>((n16 + 255) / 256, (long long)h->sm_count * 8);
+    xmc::weight_stats_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const uint4*>(h->w_ptrs[wc]), n16, h->stats,
+                                                     reinterpret_cast<unsigned int*>(h->stats + 4));
+    CU_TRY(cudaGetLastError());
+  }
+  unsigned long long host[8];
+  CU_TRY(cudaMemcpyAsync(host, h->stats, sizeof(host), cudaMemcpyDeviceToHost, st));
+  CU_TRY(cudaStreamSynchronize(st));
+  for (int i = 0; i < 4; ++i) counts[i] = (int64_t)host[i];
+  counts[4] = h->total_rows * d;
+  // magnitude byte -> value: exponent field e, mantissa m: e ? 2^(e-7) (1 + m/8) : m 2^-9
+  const unsigned int mb = (unsigned int)(host[4] & 0x7Fu);
+  const int e = (int)(mb >> 3), m = (int)(mb & 7u);
+  *amax_stored = e ? ldexpf(1.0f + (float)m / 8.0f, e - 7) : ldexpf((float)m, -9);
+  return XMC_OK;
+}
+
+int xmc_rescale(xmc_handle* h, int32_t shift, int32_t stochastic, uint64_t seed, uint64_t step, void* stream) {
+  if (h == nullptr) return fail(XMC_ERR_INVALID, "null handle");
+  if (h->w_ptrs.empty()) return fail(XMC_ERR_STATE, "xmc_bind_weights has not been called");
+  if (h->cfg.mode == XMC_MODE_BF16) return fail(XMC_ERR_STATE, "the per-tensor scale belongs to e4m3 weights");
+  if (shift < -16 || shift > 16) return fail(XMC_ERR_INVALID, "shift %d outside [-16, 16]", shift);
+  if (h->kahan != nullptr && shift != 0) return fail(XMC_ERR_STATE, "rescaling with a Kahan head bound is not defined");
+  if (shift == 0) return XMC_OK;
+  DeviceGuard guard(h->cfg.device);
+  cudaStream_t st = (cudaStream_t)stream;
+  const int d = h->cfg.dim;
+  const float factor = ldexpf(1.0f, -shift);
+  int64_t row_base = 0;
+  for (size_t wc = 0; wc < h->w_ptrs.size(); ++wc) {
+    const long long n8 = (long long)h->w_rows[wc] * d / 8;
+    const int blocks = (int)std::min<long long>((n8 + 255) / 256, (long long)h->sm_count * 8);
+    xmc::rescale_e4m3_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<uint2*>(h->w_ptrs[wc]), n8, factor, stochastic ? 1 : 0,
+                                                     seed, step, (unsigned long long)(h->cfg.label_offset + row_base) * d);
+    CU_TRY(cudaGetLastError());
+    row_base += h->w_rows[wc];
+  }
+  h->cfg.w_scale = ldexpf(h->cfg.w_scale, shift);
+  return XMC_OK;
+}
+
+float xmc_get_scale(const xmc_handle* h) { return h ? h->cfg.w_scale : 0.f; }
+
+int xmc_set_scale(xmc_handle* h, float scale) {
+  if (h == nullptr) return fail(XMC_ERR_INVALID, "null handle");
+  if (!(scale > 0.f)) return fail(XMC_ERR_INVALID, "w_scale must be positive");
+  h->cfg.w_scale = scale;
   return XMC_OK;
 }
 

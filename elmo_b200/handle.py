@@ -141,6 +141,28 @@ class XmcHandle:
         _lib.check(self.lib.xmc_profile(self._h, int(enable), None, None))
         return None
 
+    def weight_stats(self):
+        """One pass over the stored e4m3 weights (synchronises): dict of counts and fractions."""
+        counts = (C.c_int64 * 5)()
+        amax = C.c_float()
+        _lib.check(self.lib.xmc_weight_stats(self._h, counts, C.byref(amax), self._stream()))
+        n = max(int(counts[4]), 1)
+        return {"zeros": int(counts[0]), "subnormal": int(counts[1]), "saturated": int(counts[2]),
+                "nan": int(counts[3]), "elements": int(counts[4]), "amax_stored": float(amax.value),
+                "frac_zero": counts[0] / n, "frac_subnormal": counts[1] / n, "frac_saturated": counts[2] / n,
+                "scale": self.w_scale}
+
+    def rescale(self, shift: int, *, stochastic: bool = True, seed: int = 0, step: int = 0):
+        """scale <- scale * 2^shift, stored <- round(stored * 2^-shift) (real values unchanged)."""
+        _lib.check(self.lib.xmc_rescale(self._h, int(shift), int(stochastic), int(seed) & (2 ** 64 - 1),
+                                        int(step) & (2 ** 64 - 1), self._stream()))
+        self.w_scale = float(self.lib.xmc_get_scale(self._h))
+
+    def set_scale(self, scale: float):
+        """Declare the scale the stored weights are expressed in (checkpoint restore); rewrites nothing."""
+        _lib.check(self.lib.xmc_set_scale(self._h, float(scale)))
+        self.w_scale = float(scale)
+
     def check(self):
         """Synchronise the current stream and raise if a kernel flagged an error."""
         _lib.check(self.lib.xmc_check(self._h, self._stream()))

@@ -4,12 +4,17 @@
 
 Same constructor ``(cfg)``, padding rule, attributes and methods as the reference.  New optional
 config keys (defaults reproduce the reference): ``training.xmc.rounding`` ('sr' | 'rn'),
-``training.xmc.w_scale`` (per-tensor scale, stored = real / w_scale), ``model.xmc.sched_labels``.
+``training.xmc.w_scale`` (per-tensor scale, stored = real / w_scale; a number, or 'auto' to derive it
+from the initialisation bound), ``training.xmc.scale_interval`` (steps between checks of the scale
+keeper, 0 = the scale never changes), ``model.xmc.sched_labels``.
 """
+import math
+
 import torch
 from torch import nn
 
 from ..handle import XmcHandle
+from ..scale import ScaleKeeper, initial_scale
 from ._common import as_labels, cfg_get, draw_base_seed
 
 
@@ -27,7 +32,11 @@ class Fp8XMCBCEChunkedLayer(nn.Module):
         assert self.num_labels_i % 16 == 0
         d = cfg.model.xmc.input_features
         self.input_features = d
-        self.w_scale = float(cfg_get(cfg, 'training.xmc.w_scale', 1.0))
+        w_scale = cfg_get(cfg, 'training.xmc.w_scale', 1.0)
+        if w_scale == 'auto':                 # Xavier-uniform bound sqrt(6 / (fan_in + fan_out))
+            w_scale = initial_scale((6.0 / (d + self.num_labels)) ** 0.5)
+        self.w_scale = float(w_scale)
+        self.scale_keeper = ScaleKeeper(int(cfg_get(cfg, 'training.xmc.scale_interval', 0)))
         xfc_weight = torch.empty(self.num_labels, d, dtype=torch.float32)
         nn.init.xavier_uniform_(xfc_weight)                                            # :29-30
         if self.w_scale != 1.0:
@@ -87,6 +96,8 @@ class Fp8XMCBCEChunkedLayer(nn.Module):
                           grad_bf16=self._grad_buf, loss_out=self._loss_dev)
         self.iteration += 1
         self.grad_input = self._grad_buf[:bsz]
+        if self.scale_keeper.interval > 0 and self.scale_keeper.maybe_update(self._handle, self.iteration, self.base_seed):
+            self.w_scale = self._handle.w_scale
         return 0 if skip_loss else float(self._loss_dev.item())
 
     # --- checkpoint: the weights travel in state_dict as in the reference (runner.py:242-251); what the
@@ -98,8 +109,17 @@ class Fp8XMCBCEChunkedLayer(nn.Module):
     def set_extra_state(self, state):
         if not state:
             return
-        if float(state.get("w_scale", self.w_scale)) != self.w_scale:
-            raise ValueError(f"checkpoint was written with w_scale={state['w_scale']}, layer has {self.w_scale}")
+        saved = float(state.get("w_scale", self.w_scale))
+        if saved != self.w_scale:
+            # the stored weights of the checkpoint belong to ITS scale (the keeper may have moved it):
+            # adopt it, which is exact because scales are powers of two apart
+            ratio = saved / self.w_scale
+            shift = round(math.log2(ratio)) if ratio > 0 else None
+            if shift is None or 2.0 ** shift != ratio:
+                raise ValueError(f"checkpoint was written with w_scale={saved}, layer has {self.w_scale}")
+            self._handle.bind(self._weights())
+            self._handle.set_scale(saved)
+            self.w_scale = saved
         self.base_seed = int(state.get("base_seed", self.base_seed))
         self.iteration = int(state.get("iteration", self.iteration))
         self.rounding = state.get("rounding", self.rounding)

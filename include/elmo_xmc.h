@@ -134,6 +134,26 @@ int xmc_forward_topk(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batc
                      int64_t n_out, float* vals, int32_t* idx, void* stream);
 
 /*
+ * Per-tensor scale bookkeeping (e4m3 modes).  The reference has none -- its scale is the constant 1.0
+ * (src/xmc_classifiers/chunked_fp8xmc_clf.py:101-102) and Xavier-initialised weights of a 670 K-label
+ * layer land on three e4m3 values (:29-32) -- so these calls have no counterpart there.
+ *
+ * xmc_weight_stats: one pass over the bound weights; synchronises `stream`.  counts (HOST array of 5):
+ *   [0] zeros, [1] sub-normal magnitudes (0 < |w| < 2^-6 stored), [2] values at +-448, [3] NaN, [4] all
+ *   elements; amax_stored (HOST float): largest stored magnitude.
+ * xmc_rescale: scale <- scale * 2^shift and stored <- round(stored * 2^-shift), so that real weights keep
+ *   their values: shift > 0 makes room at the top (what falls below the grid is rounded, to nearest or
+ *   stochastically with the (seed, step) Philox stream), shift < 0 lifts small values into the normal
+ *   range (exact up to saturation at +-448).  Subsequent steps use the new scale.
+ * xmc_get_scale / xmc_set_scale: the scale in use; setting it declares what the stored weights mean
+ *   (checkpoint restore) and rewrites nothing.
+ */
+int xmc_weight_stats(xmc_handle* h, int64_t* counts, float* amax_stored, void* stream);
+int xmc_rescale(xmc_handle* h, int32_t shift, int32_t stochastic, uint64_t seed, uint64_t step, void* stream);
+float xmc_get_scale(const xmc_handle* h);
+int xmc_set_scale(xmc_handle* h, float scale);
+
+/*
  * Synchronise `stream`, then read and clear the device status word.  Returns XMC_OK, or
  * XMC_ERR_DEVICE_FLAG with details in xmc_last_error (bounded wait expired inside a kernel,
  * label row >= batch, ...).
