@@ -108,12 +108,13 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def layer_cfg(wl, device, batch, num_labels=None, num_chunks=None, sched=0):
+def layer_cfg(wl, device, batch, num_labels=None, num_chunks=None, sched=0, fp8_dw=False):
     return NS(environment=NS(device=str(device)),
               model=NS(xmc=NS(dtype="bfloat16", num_chunks=num_chunks or wl.num_chunks, input_features=wl.dim,
                               sched_labels=sched)),
               training=NS(precision=NS(mode="mixed", purelp_dtype="bfloat16"),
-                          xmc=NS(momentum=0, wd=0.0, simulated_fp8=(wl.mode == "simfp8"), rounding=wl.rounding),
+                          xmc=NS(momentum=0, wd=0.0, simulated_fp8=(wl.mode == "simfp8"), rounding=wl.rounding,
+                                 fp8_dw=fp8_dw),
                           FP8=NS(using_head_kahan=False, fp8_head_kahan=False, head_ratio=0.0)),
               data=NS(num_labels=num_labels or wl.num_labels, batch_size=batch))
 
@@ -288,7 +289,7 @@ def run_ours(args, wl, rank, local_rank, world):
                 blk = layer.xfc_weight[s0:s0 + 65536]
                 blk.copy_(synth.make_weights_f32(blk.shape[0], wl.dim, gen).to(torch.bfloat16))
         else:
-            layer = Fp8XMCBCEChunkedLayer(layer_cfg(wl, device, b_loc, sched=args.sched))
+            layer = Fp8XMCBCEChunkedLayer(layer_cfg(wl, device, b_loc, sched=args.sched, fp8_dw=(args.backward == "fp8dw")))
             fill_weights([p.data for p in layer.xfc_weight], wl.dim, seed=0)
             assert layer.num_labels == n_rows
         handle = layer._handle
@@ -407,7 +408,9 @@ def run_ours(args, wl, rank, local_rank, world):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
         "scaling": args.scaling, "vs_baseline": None,
         "dtype": ("bf16 weights; all contractions bf16 x bf16, fp32 accumulate" if wl.mode == "bf16" else
-                  "e4m3 weights; forward e4m3 x e4m3, backward bf16 x bf16, fp32 accumulate" if wl.mode == "fp8" else
+                  ("e4m3 weights; forward and dW e4m3 x e4m3, grad_X bf16 x bf16, fp32 accumulate (variant, not the reference's arithmetic)"
+                   if args.backward == "fp8dw" else
+                   "e4m3 weights; forward e4m3 x e4m3, backward bf16 x bf16, fp32 accumulate") if wl.mode == "fp8" else
                   "e4m3 weights up-converted to bf16; all contractions bf16 x bf16, fp32 accumulate"),
         "data": "synthetic", "config": cfg, "clocks": clocks,
         "sustained": {"ms_per_step": sus_ms, "value": B / (sus_ms * 1e-3), "unit": UNIT,
@@ -509,6 +512,9 @@ def main():
     ap.add_argument("--pass", dest="which", default="train", choices=["train", "topk"],
                     help="train = the layer's train step (default); topk = the fused top-k inference pass")
     ap.add_argument("--topk", type=int, default=5)
+    ap.add_argument("--backward", default="bf16", choices=["bf16", "fp8dw"],
+                    help="bf16 = the reference's backward arithmetic (default); fp8dw = e4m3 operands in the dW "
+                         "contraction (one GPU; a variant line, not the headline)")
     ap.add_argument("--global-batch", type=int, default=0,
                     help="fix the GLOBAL batch (per-rank batch = this / N): strong scaling instead of the default weak scaling")
     args = ap.parse_args()

@@ -12,7 +12,7 @@ from . import build as _build
 XMC_OK = 0
 DT_BF16, DT_E4M3, DT_F32, DT_E5M2 = 0, 1, 2, 3
 MODE_BF16, MODE_FP8, MODE_SIMFP8 = 0, 1, 2
-STEP_COMPUTE_LOSS, STEP_STOCHASTIC, STEP_ROUND_DW_BF16 = 1, 2, 4
+STEP_COMPUTE_LOSS, STEP_STOCHASTIC, STEP_ROUND_DW_BF16, STEP_FP8_DW = 1, 2, 4, 8
 
 
 class XmcConfig(C.Structure):

@@ -12,7 +12,7 @@ namespace xmc {
 template <bool IN_E4M3>
 __global__ void prep_x_kernel(const void* __restrict__ x, int batch, int bpad, int d,
                               uint8_t* __restrict__ x8, __nv_bfloat16* __restrict__ x16,
-                              __nv_bfloat16* __restrict__ xt) {
+                              __nv_bfloat16* __restrict__ xt, uint8_t* __restrict__ xt8) {
   __shared__ float tile[32][33];
   const int c0 = blockIdx.x * 32, b0 = blockIdx.y * 32;
   for (int i = threadIdx.y; i < 32; i += blockDim.y) {
@@ -33,10 +33,13 @@ __global__ void prep_x_kernel(const void* __restrict__ x, int batch, int bpad, i
     }
   }
   __syncthreads();
-  if (xt != nullptr) {
+  if (xt != nullptr || xt8 != nullptr) {
     for (int i = threadIdx.y; i < 32; i += blockDim.y) {
       const int c = c0 + i, b = b0 + threadIdx.x;
-      if (c < d && b < bpad) xt[(size_t)c * bpad + b] = __float2bfloat16_rn(tile[threadIdx.x][i]);
+      if (c < d && b < bpad) {
+        if (xt != nullptr) xt[(size_t)c * bpad + b] = __float2bfloat16_rn(tile[threadIdx.x][i]);
+        if (xt8 != nullptr) xt8[(size_t)c * bpad + b] = (uint8_t)(float2_to_e4m3x2(tile[threadIdx.x][i], 0.f) & 0xFFu);
+      }
     }
   }
 }
@@ -311,31 +314,41 @@ __global__ void topk_init_kernel(int* __restrict__ list_cnt, float* __restrict__
   if (i < rows) row_thr[i] = 0x007FFFFFu;                // ordered key of -inf
 }
 
-// Final top-k of one batch row from the candidate lists of the top-k launches.  One block per row.
+// Selection over the candidate lists of one batch row.  One block per row.
 // The row's lists are (CTA c with c % n_mtiles == row tile, the two epilogue warps of the row's TMEM
-// quarter, lane).  Candidates below the row's published threshold cannot be among the k best and are
-// dropped while the rest is gathered into shared memory; then k rounds of "block-wide best remaining
-// candidate" (value descending, id ascending).  If the gathered set does not fit, the rounds run over
-// the lists in global memory instead.
-constexpr int kTopkGather = 4096;
+// quarter, lane).  A candidate becomes a 64-bit key: ordered value in the high word, ~label in the low
+// word, so that a larger key means a larger value and, among equal values, the lower label; labels are
+// unique, hence keys are.  The k-th largest key is found by a radix select, eight bits at a time (eight
+// passes of a 256-bin histogram over the candidates that still match the digits chosen so far).
+//   FINAL = false  mid-course pass between launches: publish the k-th best value seen so far as the row's
+//                  threshold (nothing below it can end up among the k best), so that later launches
+//                  append few candidates and rarely have to cut a list back;
+//   FINAL = true   collect the k keys at or above the k-th, sort them, write (value desc, label asc).
+// Candidates at or above the row's published threshold are first gathered into shared memory (key_cap
+// keys); if they do not fit, every pass walks the lists in global memory instead.
+__device__ __forceinline__ unsigned long long topk_key64(float v, int id) {
+  const unsigned int bits = __float_as_uint(v);
+  const unsigned int ord = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+  return ((unsigned long long)ord << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned int)id);
+}
+template <bool FINAL>
 __global__ void __launch_bounds__(256)
-topk_merge_kernel(const float* __restrict__ cand_val, int* __restrict__ cand_idx, const int* __restrict__ list_cnt,
-                  const unsigned int* __restrict__ row_thr, int cap, int grid, int n_mtiles, int k, int batch,
-                  long long label_offset, float* __restrict__ out_val, int* __restrict__ out_idx) {
+topk_select_kernel(const float* __restrict__ cand_val, const int* __restrict__ cand_idx, const int* __restrict__ list_cnt,
+                   unsigned int* __restrict__ row_thr, int cap, int grid, int n_mtiles, int k, int batch,
+                   long long label_offset, float* __restrict__ out_val, int* __restrict__ out_idx, int key_cap) {
+  extern __shared__ unsigned long long sel_smem[];
+  unsigned long long* keys = sel_smem;                   // [key_cap]
+  unsigned long long* outk = sel_smem + key_cap;         // [128]
+  __shared__ int hist[256];
+  __shared__ int s_total, s_need, s_digit, s_nout;
   const int b = blockIdx.x;
   if (b >= batch) return;
   const int mt = b >> 7, q = (b >> 5) & 3, lane = b & 31;
   const int ctas = grid / n_mtiles;                     // CTAs that worked on this row's batch tile
   const int lists = ctas * 2;                           // two epilogue warps (column phases) per quarter
-  __shared__ float g_val[kTopkGather];
-  __shared__ int g_id[kTopkGather];
-  __shared__ int g_n;
-  __shared__ float s_val[8];
-  __shared__ int s_pos[8];
-  __shared__ int s_id[8];
-  unsigned int key = row_thr[b];
-  const float g = (key & 0x80000000u) ? __uint_as_float(key & 0x7FFFFFFFu) : __uint_as_float(~key);
-  if (threadIdx.x == 0) g_n = 0;
+  const unsigned int tkey = row_thr[b];
+  const float g = (tkey & 0x80000000u) ? __uint_as_float(tkey & 0x7FFFFFFFu) : __uint_as_float(~tkey);
+  if (threadIdx.x == 0) { s_total = 0; s_nout = 0; }
   __syncthreads();
   auto list_of = [&](int r) {
     const int c = (r >> 1) * n_mtiles + mt, ph = r & 1;
@@ -345,73 +358,96 @@ topk_merge_kernel(const float* __restrict__ cand_val, int* __restrict__ cand_idx
       if (((sl + 2) & 3) == q) slot = sl;
     return (c * 8 + slot) * 32 + lane;
   };
-  for (int r = threadIdx.x; r < lists; r += blockDim.x) {
-    const int li = list_of(r);
-    const int n = list_cnt[li];
-    for (int e = 0; e < n; ++e) {
-      const float v = cand_val[(size_t)li * (cap + 32) + e];
-      if (v >= g) {
-        const int at = atomicAdd(&g_n, 1);
-        if (at < kTopkGather) {
-          g_val[at] = v;
-          g_id[at] = cand_idx[(size_t)li * (cap + 32) + e];
+  // visit every candidate at or above the published threshold, from the lists in global memory
+  auto for_each_global = [&](auto&& f) {
+    for (int r = threadIdx.x; r < lists; r += blockDim.x) {
+      const size_t base = (size_t)list_of(r) * (cap + 32);
+      const int n = list_cnt[list_of(r)];
+      for (int e = 0; e < n; ++e) {
+        const float v = cand_val[base + e];
+        if (v >= g) f(topk_key64(v, cand_idx[base + e]));
+      }
+    }
+  };
+  for_each_global([&](unsigned long long key) {
+    const int at = atomicAdd(&s_total, 1);
+    if (at < key_cap) keys[at] = key;
+  });
+  __syncthreads();
+  const int total = s_total;
+  const bool in_smem = total <= key_cap;
+  auto for_each = [&](auto&& f) {
+    if (in_smem) {
+      for (int t = threadIdx.x; t < total; t += blockDim.x) f(keys[t]);
+    } else {
+      for_each_global(f);
+    }
+  };
+  unsigned long long kth = 0ull;                         // every key is >= 0: with fewer than k candidates all are taken
+  if (total > k) {
+    unsigned long long prefix = 0ull, mask = 0ull;
+    if (threadIdx.x == 0) s_need = k;
+    for (int shift = 56; shift >= 0; shift -= 8) {
+      hist[threadIdx.x] = 0;
+      __syncthreads();
+      for_each([&](unsigned long long key) {
+        if ((key & mask) == prefix) atomicAdd(&hist[(int)((key >> shift) & 0xFFull)], 1);
+      });
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        int need = s_need, d = 255;
+        for (; d > 0; --d) {
+          if (hist[d] >= need) break;
+          need -= hist[d];
+        }
+        s_need = need;
+        s_digit = d;
+      }
+      __syncthreads();
+      prefix |= (unsigned long long)s_digit << shift;
+      mask |= 0xFFull << shift;
+    }
+    kth = prefix;
+  }
+  if (!FINAL) {
+    // the value part of the k-th best key is a valid lower bound of the row's final k-th value
+    if (threadIdx.x == 0 && total >= k) atomicMax(&row_thr[b], (unsigned int)(kth >> 32));
+    return;
+  }
+  for_each([&](unsigned long long key) {
+    if (key >= kth) {
+      const int at = atomicAdd(&s_nout, 1);
+      if (at < 128) outk[at] = key;
+    }
+  });
+  __syncthreads();
+  const int n_out = min(s_nout, k);
+  if (threadIdx.x < 128 && threadIdx.x >= n_out) outk[threadIdx.x] = 0ull;
+  __syncthreads();
+  // bitonic sort of 128 keys, descending
+  for (int size = 2; size <= 128; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      if (threadIdx.x < 128) {
+        const int i = threadIdx.x, j = i ^ stride;
+        if (j > i) {
+          const unsigned long long a = outk[i], c = outk[j];
+          const bool desc = (i & size) == 0;
+          if (desc ? a < c : a > c) { outk[i] = c; outk[j] = a; }
         }
       }
+      __syncthreads();
     }
   }
-  __syncthreads();
-  const int total = g_n;
-  const bool in_smem = total <= kTopkGather;
-  const int w = threadIdx.x >> 5, ln = threadIdx.x & 31;
-  for (int round = 0; round < k; ++round) {
-    float best = -INFINITY;
-    int best_pos = -1, best_id = 0x7fffffff;
-    if (in_smem) {
-      for (int t = threadIdx.x; t < total; t += blockDim.x) {
-        const float v = g_val[t];
-        const int id = g_id[t];
-        if (id >= 0 && (v > best || (v == best && id < best_id) || best_pos < 0)) { best = v; best_pos = t; best_id = id; }
-      }
+  if (threadIdx.x < k) {
+    const unsigned long long key = outk[threadIdx.x];
+    if ((int)threadIdx.x < n_out) {
+      const unsigned int ord = (unsigned int)(key >> 32);
+      out_val[(size_t)b * k + threadIdx.x] = __uint_as_float((ord & 0x80000000u) ? (ord & 0x7FFFFFFFu) : ~ord);
+      out_idx[(size_t)b * k + threadIdx.x] = (int)(label_offset + (long long)(0xFFFFFFFFu - (unsigned int)(key & 0xFFFFFFFFull)));
     } else {
-      for (int r = threadIdx.x; r < lists; r += blockDim.x) {
-        const int li = list_of(r);
-        const int n = list_cnt[li];
-        for (int e = 0; e < n; ++e) {
-          const float v = cand_val[(size_t)li * (cap + 32) + e];
-          const int id = cand_idx[(size_t)li * (cap + 32) + e];
-          if (id >= 0 && (v > best || (v == best && id < best_id) || best_pos < 0)) { best = v; best_pos = li * (cap + 32) + e; best_id = id; }
-        }
-      }
+      out_val[(size_t)b * k + threadIdx.x] = -INFINITY;
+      out_idx[(size_t)b * k + threadIdx.x] = -1;
     }
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      const int op = __shfl_xor_sync(0xffffffffu, best_pos, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, best_id, o);
-      if (op >= 0 && (best_pos < 0 || ov > best || (ov == best && oi < best_id))) { best = ov; best_pos = op; best_id = oi; }
-    }
-    if (ln == 0) { s_val[w] = best; s_pos[w] = best_pos; s_id[w] = best_id; }
-    __syncthreads();
-    if (w == 0) {
-      const int nw = blockDim.x >> 5;
-      best = ln < nw ? s_val[ln] : -INFINITY;
-      best_pos = ln < nw ? s_pos[ln] : -1;
-      best_id = ln < nw ? s_id[ln] : 0x7fffffff;
-      for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-        const int op = __shfl_xor_sync(0xffffffffu, best_pos, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, best_id, o);
-        if (op >= 0 && (best_pos < 0 || ov > best || (ov == best && oi < best_id))) { best = ov; best_pos = op; best_id = oi; }
-      }
-      if (ln == 0) {
-        out_val[(size_t)b * k + round] = best_pos >= 0 ? best : -INFINITY;
-        out_idx[(size_t)b * k + round] = best_pos >= 0 ? (int)(label_offset + best_id) : -1;
-        if (best_pos >= 0) {                                              // consumed
-          if (in_smem) g_id[best_pos] = -1;
-          else cand_idx[best_pos] = -1;
-        }
-      }
-    }
-    __syncthreads();
   }
 }
 

@@ -233,6 +233,9 @@ struct xmc_handle {
   __nv_bfloat16* x16 = nullptr;    // [max(bpad_max,256) x d]
   __nv_bfloat16* xt = nullptr;     // [max(d,256) x bpad_max]
   __nv_bfloat16* G = nullptr;      // [sched x bpad_max]
+  uint8_t* G8 = nullptr;           // [sched x bpad_max] e4m3(G * 256), allocated when the FP8 dW contraction is first asked for
+  uint8_t* xt8 = nullptr;          // [max(d,256) x bpad_max] e4m3 X transposed, likewise
+  int64_t g8_rows = 0;
   __nv_bfloat16* w16 = nullptr;    // [sched x d] bf16 staging of an e4m3 chunk
   float* partial = nullptr;
   int64_t partial_floats = 0;
@@ -315,16 +318,18 @@ xmc::BucketGeom geom_of(const xmc_handle* h) {
 }
 
 int prep_x(xmc_handle* h, const void* x, int x_dtype, int batch, int bpad, bool need_x8, bool need_x16,
-           bool need_xt, cudaStream_t st) {
+           bool need_xt, cudaStream_t st, bool need_xt8 = false) {
   const int d = h->cfg.dim;
   dim3 grid(cdiv(d, 32), cdiv(bpad, 32)), block(32, 8);
   mark(h, K_PREP, st);
   if (x_dtype == XMC_DT_E4M3)
     xmc::prep_x_kernel<true><<<grid, block, 0, st>>>(x, batch, bpad, d, need_x8 ? h->x8 : nullptr,
-                                                     need_x16 ? h->x16 : nullptr, need_xt ? h->xt : nullptr);
+                                                     need_x16 ? h->x16 : nullptr, need_xt ? h->xt : nullptr,
+                                                     need_xt8 ? h->xt8 : nullptr);
   else
     xmc::prep_x_kernel<false><<<grid, block, 0, st>>>(x, batch, bpad, d, need_x8 ? h->x8 : nullptr,
-                                                      need_x16 ? h->x16 : nullptr, need_xt ? h->xt : nullptr);
+                                                      need_x16 ? h->x16 : nullptr, need_xt ? h->xt : nullptr,
+                                                      need_xt8 ? h->xt8 : nullptr);
   CU_TRY(cudaGetLastError());
   return XMC_OK;
 }
@@ -400,7 +405,7 @@ int xmc_destroy(xmc_handle* h) {
   if (h == nullptr) return XMC_OK;
   DeviceGuard guard(h->cfg.device);
   if (h->l2_persist_bytes > 0) cudaCtxResetPersistingL2Cache();   // lines pinned for the partial sums become normal again
-  void* ptrs[] = {h->x8, h->x16, h->xt, h->G, h->w16, h->partial, h->bucket_cnt, h->bucket_off,
+  void* ptrs[] = {h->x8, h->x16, h->xt, h->G, h->G8, h->xt8, h->w16, h->partial, h->bucket_cnt, h->bucket_off,
                   h->entries, h->loss_partial, h->status, h->stats, h->topk_val, h->topk_idx, h->topk_cnt, h->topk_thr, h->topk_max, h->topk_row};
   for (void* p : ptrs)
     if (p != nullptr) cudaFree(p);
@@ -437,6 +442,7 @@ int xmc_bind_weights(xmc_handle* h, int32_t n_chunks, void* const* ptrs, const i
   if (g_rows > h->g_rows) {
     const int d = h->cfg.dim;
     if (h->G) { cudaFree(h->G); h->ws_bytes -= h->g_rows * h->bpad_max * 2; h->G = nullptr; }
+    if (h->G8) { cudaFree(h->G8); h->ws_bytes -= h->g8_rows * h->bpad_max; h->G8 = nullptr; h->g8_rows = 0; }
     if (h->w16) { cudaFree(h->w16); h->ws_bytes -= h->g_rows * d * 2; h->w16 = nullptr; }
     h->g_rows = 0;
     if (int rc = dev_alloc(h, (void**)&h->G, (size_t)g_rows * h->bpad_max * 2, true)) return rc;
@@ -577,9 +583,24 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
   const bool fwd_fp8 = mode == XMC_MODE_FP8;
   const bool want_loss = (flags & XMC_STEP_COMPUTE_LOSS) != 0;
   const bool sr = (flags & XMC_STEP_STOCHASTIC) != 0;
+  const bool dw8 = (flags & XMC_STEP_FP8_DW) != 0;
+  if (dw8) {
+    if (!fwd_fp8) return fail(XMC_ERR_STATE, "the FP8 dW contraction belongs to the real-FP8 mode");
+    if ((flags & XMC_STEP_ROUND_DW_BF16) || wd != 0.f || h->kahan != nullptr)
+      return fail(XMC_ERR_STATE, "the FP8 dW contraction takes no weight decay, bf16 dW rounding or Kahan head");
+    if (h->G8 == nullptr || h->g8_rows < h->g_rows) {
+      CU_TRY(cudaStreamSynchronize(st));
+      if (h->G8) { cudaFree(h->G8); h->ws_bytes -= h->g8_rows * h->bpad_max; h->G8 = nullptr; }
+      if (int rc = dev_alloc(h, (void**)&h->G8, (size_t)h->g_rows * h->bpad_max, true)) return rc;
+      h->g8_rows = h->g_rows;
+    }
+    if (h->xt8 == nullptr) {
+      if (int rc = dev_alloc(h, (void**)&h->xt8, (size_t)std::max(h->cfg.dim, 256) * h->bpad_max, true)) return rc;
+    }
+  }
 
   // --- embeddings: e4m3 copy (forward), bf16 copy, bf16 transpose (update) ---
-  if (int rc = prep_x(h, x, x_dtype, batch, bpad, fwd_fp8, !fwd_fp8, true, st)) return rc;
+  if (int rc = prep_x(h, x, x_dtype, batch, bpad, fwd_fp8, !fwd_fp8, !dw8, st, dw8)) return rc;
 
   // --- bucket the positives by label tile ---
   if (nnz > h->ent_cap) {
@@ -639,8 +660,13 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
   } else {
     if (int rc = make_map_kmajor(&map_x, false, h->x16, d, xrows, d, 256)) return rc;
   }
-  if (int rc = make_map_kmajor(&map_xt, false, h->xt, bpad, std::max(d, 256), bpad, 256)) return rc;
-  if (int rc = make_map_kmajor(&map_g_k, false, h->G, bpad, h->g_rows, bpad, 128)) return rc;
+  if (dw8) {
+    if (int rc = make_map_kmajor(&map_xt, true, h->xt8, bpad, std::max(d, 256), bpad, 256)) return rc;
+    if (int rc = make_map_kmajor(&map_g_k, true, h->G8, bpad, h->g8_rows, bpad, 128)) return rc;
+  } else {
+    if (int rc = make_map_kmajor(&map_xt, false, h->xt, bpad, std::max(d, 256), bpad, 256)) return rc;
+    if (int rc = make_map_kmajor(&map_g_k, false, h->G, bpad, h->g_rows, bpad, 128)) return rc;
+  }
   if (int rc = make_map_blocked(&map_g_mn, false, h->G, bpad, h->g_rows, bpad, xmc::kGxRows, true)) return rc;
 
   const float lr_eff = lr / h->cfg.w_scale;
@@ -688,6 +714,7 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
       fp.k_steps = cdiv((long long)d * (fwd_fp8 ? 1 : 2), 128);
       fp.w_scale = h->cfg.w_scale;
       fp.G = h->G;
+      fp.G8 = h->G8;
       fp.bucket_off = h->bucket_off;
       fp.bucket_ent = h->entries;
       fp.tile_base = ((int)wc * spc + sc) * tiles_per_sched;
@@ -700,8 +727,10 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
       }
       int rc;
       mark(h, K_FWD, st);
-      if (fwd_fp8) rc = want_loss ? launch_gemm<xmc::FwdPolicy<true, true>>(map_w, map_x, fp, f_tiles, h->sm_count, st)
-                                  : launch_gemm<xmc::FwdPolicy<true, false>>(map_w, map_x, fp, f_tiles, h->sm_count, st);
+      if (dw8) rc = want_loss ? launch_gemm<xmc::FwdPolicy<true, true, true>>(map_w, map_x, fp, f_tiles, h->sm_count, st)
+                              : launch_gemm<xmc::FwdPolicy<true, false, true>>(map_w, map_x, fp, f_tiles, h->sm_count, st);
+      else if (fwd_fp8) rc = want_loss ? launch_gemm<xmc::FwdPolicy<true, true>>(map_w, map_x, fp, f_tiles, h->sm_count, st)
+                                       : launch_gemm<xmc::FwdPolicy<true, false>>(map_w, map_x, fp, f_tiles, h->sm_count, st);
       else rc = want_loss ? launch_gemm<xmc::FwdPolicy<false, true>>(map_w, map_x, fp, f_tiles, h->sm_count, st)
                           : launch_gemm<xmc::FwdPolicy<false, false>>(map_w, map_x, fp, f_tiles, h->sm_count, st);
       if (rc) return rc;
@@ -743,9 +772,9 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
       up.n_ltiles = n_lt;
       up.n_dtiles = n_dt;
       up.d = d;
-      up.k_steps = cdiv(bpad, 64);
+      up.k_steps = cdiv(bpad, dw8 ? 128 : 64);
       up.W = wbase;
-      up.lr_eff = lr_eff;
+      up.lr_eff = dw8 ? lr_eff / xmc::kG8Scale : lr_eff;
       up.wd = wd;
       up.seed = seed;
       up.step = step;
@@ -778,7 +807,10 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
       const CUtensorMap* wt = w8 ? &map_wt : nullptr;
 #define XMC_UPD(W8_, SR_, RD_, WD_) \
   launch_gemm<xmc::UpdPolicy<W8_, SR_, RD_, WD_>>(map_g_k, map_xt, up, u_tiles, h->sm_count, st, 0, wt)
-      if (kahan_here) {
+      if (dw8) {
+        rc = sr ? launch_gemm<xmc::UpdPolicy<true, true, false, false, false, true>>(map_g_k, map_xt, up, u_tiles, h->sm_count, st, 0, wt)
+                : launch_gemm<xmc::UpdPolicy<true, false, false, false, false, true>>(map_g_k, map_xt, up, u_tiles, h->sm_count, st, 0, wt);
+      } else if (kahan_here) {
         rc = sr ? launch_gemm<xmc::UpdPolicy<true, true, false, false, true>>(map_g_k, map_xt, up, u_tiles, h->sm_count, st, 0, wt)
                 : launch_gemm<xmc::UpdPolicy<true, false, false, false, true>>(map_g_k, map_xt, up, u_tiles, h->sm_count, st, 0, wt);
       } else if (w8) {
@@ -955,6 +987,17 @@ int xmc_forward_topk(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batc
   } else {
     if (int rc = make_map_kmajor(&map_x, false, h->x16, d, xrows, d, 128)) return rc;
   }
+  // selection kernels: up to 24 576 candidate keys of a row in shared memory (192 KB) + 128 output keys
+  constexpr int kSelKeys = 24576;
+  constexpr size_t sel_smem = (size_t)(kSelKeys + 128) * sizeof(unsigned long long);
+  {
+    static std::atomic<uint64_t> configured{0};
+    if (!((configured.load(std::memory_order_relaxed) >> (h->cfg.device & 63)) & 1ull)) {
+      CU_TRY(cudaFuncSetAttribute(xmc::topk_select_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sel_smem));
+      CU_TRY(cudaFuncSetAttribute(xmc::topk_select_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sel_smem));
+      configured.fetch_or(1ull << (h->cfg.device & 63));
+    }
+  }
   int launch = 0;
   int64_t row_base = 0;
   for (size_t wc = 0; wc < h->w_ptrs.size() && row_base < n_out; ++wc) {
@@ -972,6 +1015,17 @@ int xmc_forward_topk(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batc
                                                          reinterpret_cast<uint4*>(h->w16), n16);
         CU_TRY(cudaGetLastError());
         wsrc = h->w16;
+      }
+      // Mid-course thresholds: for k > 8 (the in-kernel k-th-of-maxima bound covers smaller k) the exact
+      // k-th best value of what the lists hold is published after launches 1, 2, 4, 8, ...; the first one
+      // turns the flood of the first launch (every logit is a candidate while nothing is known) into a
+      // threshold the rest of the call lives on.
+      if (k > 8 && launch > 0 && (launch & (launch - 1)) == 0) {
+        mark(h, K_LOGITS, st);
+        xmc::topk_select_kernel<false><<<batch, 256, sel_smem, st>>>(h->topk_val, h->topk_idx, h->topk_cnt, h->topk_row, cap,
+                                                                     grid_max, n_mt, k, batch, h->cfg.label_offset, nullptr,
+                                                                     nullptr, kSelKeys);
+        CU_TRY(cudaGetLastError());
       }
       CUtensorMap map_w;
       if (int rc = make_map_kmajor(&map_w, fwd_fp8, wsrc, d, rows, d, 256)) return rc;
@@ -1007,8 +1061,8 @@ int xmc_forward_topk(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batc
     row_base += rows_wc;
   }
   mark(h, K_LOGITS, st);
-  xmc::topk_merge_kernel<<<batch, 256, 0, st>>>(h->topk_val, h->topk_idx, h->topk_cnt, h->topk_row, cap, grid_max, n_mt, k,
-                                                batch, h->cfg.label_offset, vals, idx);
+  xmc::topk_select_kernel<true><<<batch, 256, sel_smem, st>>>(h->topk_val, h->topk_idx, h->topk_cnt, h->topk_row, cap, grid_max,
+                                                              n_mt, k, batch, h->cfg.label_offset, vals, idx, kSelKeys);
   CU_TRY(cudaGetLastError());
   mark(h, K_END, st);
   return XMC_OK;

@@ -27,6 +27,7 @@ struct FwdParams {
   int k_steps;             // cdiv(d * elem_size, 128)
   float w_scale;
   __nv_bfloat16* G;        // [n_ltiles*128 x bpad]
+  uint8_t* G8;             // WRITE_G8 variants: e4m3(G * 256), same shape (operand of the FP8 dW contraction)
   const int* bucket_off;   // positives bucketed by label tile: offsets ...
   const uint32_t* bucket_ent;  // ... entries: batch row | (label-in-tile << 16)
   int tile_base;           // bucket index of this chunk's label tile 0
@@ -34,7 +35,9 @@ struct FwdParams {
   int* status;
 };
 
-template <bool FP8, bool LOSS>
+constexpr float kG8Scale = 256.0f;      // |G| < 1: e4m3(G * 256) stays below 448
+
+template <bool FP8, bool LOSS, bool WRITE_G8 = false>
 struct FwdPolicy {
   using Params = FwdParams;
   static constexpr bool kMnMajor = false;
@@ -150,6 +153,20 @@ struct FwdPolicy {
           else if (b + 1 >= p.batch) out[i] &= 0x0000FFFFu;
         }
       }
+      if constexpr (WRITE_G8) {
+        // the same 32 values once more as e4m3(G * 256): one 32-byte sector
+        if (j.b0 + c0 < p.bpad) {
+          U32x8 g8;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t w0 = out[2 * k], w1 = out[2 * k + 1];
+            const uint32_t lo = float2_to_e4m3x2(__uint_as_float(w0 << 16) * kG8Scale, __uint_as_float(w0 & 0xFFFF0000u) * kG8Scale);
+            const uint32_t hi = float2_to_e4m3x2(__uint_as_float(w1 << 16) * kG8Scale, __uint_as_float(w1 & 0xFFFF0000u) * kG8Scale);
+            g8.v[k] = lo | (hi << 16);
+          }
+          st_global_256(p.G8 + (size_t)crow * p.bpad + j.b0 + c0, g8);
+        }
+      }
       // two 256-bit stores: every thread writes whole 32-byte sectors of its row
       __nv_bfloat16* grow = p.G + (size_t)crow * p.bpad + j.b0 + c0;
 #pragma unroll
@@ -196,13 +213,15 @@ struct UpdParams {
   int* status;
 };
 
-template <bool W8, bool SR, bool ROUND_DW, bool HAS_WD, bool KAHAN = false>
+// OPS8: the dW contraction takes e4m3 operands (G * 256 and X, both as the forward already quantises
+// them) instead of bf16 ones; the caller folds the 1/256 into lr_eff.  Off in every reference-parity path.
+template <bool W8, bool SR, bool ROUND_DW, bool HAS_WD, bool KAHAN = false, bool OPS8 = false>
 struct UpdPolicy {
   using Params = UpdParams;
   static constexpr bool kMnMajor = false;
-  static constexpr bool kFp8 = false;
-  static constexpr uint32_t kFmt = 1u;
-  static constexpr int kElemsPerRow = 64;
+  static constexpr bool kFp8 = OPS8;
+  static constexpr uint32_t kFmt = OPS8 ? 0u : 1u;
+  static constexpr int kElemsPerRow = OPS8 ? 128 : 64;
   static constexpr int kEpiWarps = 16;
   // e4m3 weights: the tile's 128 x 256 weight bytes come in by TMA while the main loop runs and go back
   // by TMA (two 32 KB slots, paid for with one operand stage: with a single slot the refill has to wait

@@ -90,7 +90,7 @@ class XmcHandle:
 
     def step(self, x: torch.Tensor, labels: Optional[torch.Tensor], lr: float, *, wd: float = 0.0,
              seed: int = 0, step: int = 0, stochastic: bool = True, compute_loss: bool = False,
-             round_dw_bf16: bool = False, grad_f32: Optional[torch.Tensor] = None,
+             round_dw_bf16: bool = False, fp8_dw: bool = False, grad_f32: Optional[torch.Tensor] = None,
              grad_bf16: Optional[torch.Tensor] = None, loss_out: Optional[torch.Tensor] = None):
         assert x.dtype == torch.bfloat16 and x.is_contiguous() and x.is_cuda and x.shape[1] == self.dim
         nnz = 0
@@ -98,7 +98,7 @@ class XmcHandle:
             assert labels.dtype == torch.int32 and labels.is_contiguous() and labels.shape[1] == 2
             nnz = labels.shape[0]
         flags = (_lib.STEP_COMPUTE_LOSS if compute_loss else 0) | (_lib.STEP_STOCHASTIC if stochastic else 0) \
-            | (_lib.STEP_ROUND_DW_BF16 if round_dw_bf16 else 0)
+            | (_lib.STEP_ROUND_DW_BF16 if round_dw_bf16 else 0) | (_lib.STEP_FP8_DW if fp8_dw else 0)
         batch = x.shape[0]
         for g, dt in ((grad_f32, torch.float32), (grad_bf16, torch.bfloat16)):
             if g is not None:

@@ -6,7 +6,8 @@ range of label rows (weights and their stochastic-rounding stream), the encoder 
 parallel:
 
     X_local [B_loc, d]  --all-gather-->  X [B, d]           (bf16, B = world * B_loc)
-    labels_local        --all-gather-->  labels [nnz, 2]    (rows shifted by rank * B_loc)
+    labels_local        --all-gather-->  labels [nnz, 2]    (rows shifted by rank * B_loc; can be started
+                                                             before the encoder runs: ``prefetch_labels``)
     local shard step on the CUDA library (forward, grad_X partial, weight update)
     grad_X [B, d] fp32  --reduce-scatter(sum)-->  grad_input [B_loc, d]
 
@@ -80,6 +81,10 @@ class LabelShardedXMC:
         self.num_rows = num_rows
         self.time_comm = time_comm          # record CUDA events around the collectives (bench bookkeeping)
         self._comm_events = []
+        self._side = None                   # stream of the prefetched label all-gather
+        self._lab_ready = None
+        self._lab_local = None
+        self._lab_prefetched = False
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.dim, self.local_batch = dim, local_batch
@@ -95,15 +100,45 @@ class LabelShardedXMC:
         self._gl = torch.zeros(local_batch, dim, dtype=torch.float32, device=self.device)
         self.grad_input = torch.zeros(local_batch, dim, dtype=torch.bfloat16, device=self.device)
 
+    def prefetch_labels(self, labels_local: Optional[torch.Tensor]):
+        """Start the all-gather of this step's labels now -- they are known before the encoder runs
+        (runner.py:139-146 moves them to the device, then calls the encoder) -- on a side stream, so that
+        it overlaps the encoder forward and only the embeddings are gathered once the encoder is done.
+        The next ``xfc_forward_backward`` / ``gather_inputs`` call must then pass ``labels_local=None``.
+        All ranks must call it (it is a collective)."""
+        lab = pad_labels(labels_local, self.capacity, self.rank * self.local_batch, self.device)
+        self._lab_prefetched = True
+        if self.world == 1:
+            self._lab_local = lab
+            return
+        if self.device.type == "cuda":
+            if self._side is None:
+                self._side = torch.cuda.Stream(self.device)
+            cur = torch.cuda.current_stream(self.device)
+            self._side.wait_stream(cur)                 # `lab` was produced on the current stream
+            with torch.cuda.stream(self._side):
+                dist.all_gather_into_tensor(self._lg, lab, group=self.group)
+                self._lab_ready = torch.cuda.Event()
+                self._lab_ready.record(self._side)
+            lab.record_stream(self._side)
+        else:
+            dist.all_gather_into_tensor(self._lg, lab, group=self.group)
+
     def gather_inputs(self, embed_local: torch.Tensor, labels_local: Optional[torch.Tensor]):
         assert embed_local.shape == (self.local_batch, self.dim)
         x = embed_local.to(torch.bfloat16).contiguous()
-        lab = pad_labels(labels_local, self.capacity, self.rank * self.local_batch, self.device)
+        pre = self._lab_prefetched and labels_local is None
+        self._lab_prefetched = False
+        lab = self._lab_local if (pre and self.world == 1) else \
+            (None if pre else pad_labels(labels_local, self.capacity, self.rank * self.local_batch, self.device))
         if self.world == 1:
             return x, lab
         with self._comm():
             dist.all_gather_into_tensor(self._xg, x, group=self.group)
-            dist.all_gather_into_tensor(self._lg, lab, group=self.group)
+            if not pre:
+                dist.all_gather_into_tensor(self._lg, lab, group=self.group)
+        if pre and self._lab_ready is not None:
+            torch.cuda.current_stream(self.device).wait_event(self._lab_ready)
         return self._xg, self._lg
 
     # --- collective timing -------------------------------------------------------------------

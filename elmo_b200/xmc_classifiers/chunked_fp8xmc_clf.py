@@ -6,7 +6,8 @@ Same constructor ``(cfg)``, padding rule, attributes and methods as the referenc
 config keys (defaults reproduce the reference): ``training.xmc.rounding`` ('sr' | 'rn'),
 ``training.xmc.w_scale`` (per-tensor scale, stored = real / w_scale; a number, or 'auto' to derive it
 from the initialisation bound), ``training.xmc.scale_interval`` (steps between checks of the scale
-keeper, 0 = the scale never changes), ``model.xmc.sched_labels``.
+keeper, 0 = the scale never changes), ``training.xmc.fp8_dw`` (FP8 operands in the dW contraction; faster,
+not the reference's arithmetic), ``model.xmc.sched_labels``.
 """
 import math
 
@@ -54,6 +55,8 @@ class Fp8XMCBCEChunkedLayer(nn.Module):
         self.grad_input = self._grad_buf
         self.iteration = 0
         self.rounding = cfg_get(cfg, 'training.xmc.rounding', 'sr')
+        # optional, off by default, not the reference's arithmetic: FP8 operands in the dW contraction
+        self.fp8_dw = bool(cfg_get(cfg, 'training.xmc.fp8_dw', False))
         self.base_seed = draw_base_seed()
         self._handle = XmcHandle(self.device, d, self.max_batch,
                                  'simfp8' if self.fake_fp8_matmul else 'fp8',
@@ -92,7 +95,7 @@ class Fp8XMCBCEChunkedLayer(nn.Module):
         self._handle.bind(self._weights())
         self._handle.step(embed.contiguous(), as_labels(labels, embed.device), xmc_lr[0],
                           seed=self.base_seed, step=self.iteration,
-                          stochastic=(self.rounding == 'sr'), compute_loss=not skip_loss,
+                          stochastic=(self.rounding == 'sr'), compute_loss=not skip_loss, fp8_dw=self.fp8_dw,
                           grad_bf16=self._grad_buf, loss_out=self._loss_dev)
         self.iteration += 1
         self.grad_input = self._grad_buf[:bsz]

@@ -53,9 +53,13 @@ enum {
 enum {
   XMC_STEP_COMPUTE_LOSS = 1,      /* skip_loss == False: write the summed BCE loss             */
   XMC_STEP_STOCHASTIC = 2,        /* stochastic rounding of W (else round-to-nearest-even)     */
-  XMC_STEP_ROUND_DW_BF16 = 4      /* round the dW accumulator to bf16 before the update, as the
+  XMC_STEP_ROUND_DW_BF16 = 4,     /* round the dW accumulator to bf16 before the update, as the
                                      reference's 'chunked' class does by materialising dW
                                      (chunked.py:119)                                            */
+  XMC_STEP_FP8_DW = 8             /* NOT the reference's arithmetic (fuse_kernel.py:88-92 multiplies
+                                     bf16 operands): the dW contraction takes e4m3 operands,
+                                     e4m3(G * 256) and e4m3(X), at twice the tensor rate.  Real-FP8
+                                     mode only; grad_X keeps its bf16 operands.  Off by default.   */
 };
 
 typedef struct xmc_handle xmc_handle;

@@ -288,7 +288,7 @@ def fp8_chunked_step(w_chunks: Sequence[torch.Tensor], x: torch.Tensor, labels: 
                      seed: int = 0, step: int = 0, w_scale: float = 1.0,
                      label_offset: int = 0, compute_loss: bool = False,
                      kahan: Optional[torch.Tensor] = None,
-                     chunk_seeds: Optional[Sequence[int]] = None,
+                     chunk_seeds: Optional[Sequence[int]] = None, fp8_dw: bool = False,
                      ) -> Tuple[List[torch.Tensor], torch.Tensor, float]:
     """One ``Fp8XMCBCEChunkedLayer.xfc_forward_backward`` (chunked_fp8xmc_clf.py:81-123).
 
@@ -298,6 +298,9 @@ def fp8_chunked_step(w_chunks: Sequence[torch.Tensor], x: torch.Tensor, labels: 
                    Philox element index, so sharded and unsharded runs draw the same bits.
     kahan    : optional compensation buffer for rows [0, num_head) of chunk 0
                (chunked_head_kahan_fp8xmc_clf.py:127-131), bf16 or e5m2; updated in place.
+    fp8_dw   : NOT the reference's arithmetic -- the build's optional FP8-operand dW contraction:
+               ``acc = e4m3(G * 256) . e4m3(X) / 256`` instead of bf16 operands (fuse_kernel.py:88-92);
+               grad_X keeps bf16 operands.  Restated here so that the variant has an oracle of its own.
     chunk_seeds : rounding 'sr_triton' only -- the seed the reference draws on the host for each
                chunk (chunked_fp8xmc_clf.py:113); offsets restart at 0 in every updated tensor.
     Returns (new chunks, grad_X fp32 [B, d] (not yet cast to bf16), loss).
@@ -330,7 +333,11 @@ def fp8_chunked_step(w_chunks: Sequence[torch.Tensor], x: torch.Tensor, labels: 
         g = torch.where(y, g - 1.0, g)                         # :108  (bf16 arithmetic)
         gx = large_k_matmul(g, w32)                            # :109-112
         grad_x += gx * s32 if s32 != 1.0 else gx
-        acc = matmul_acc(g, x32)                               # fuse_kernel.py:84-96 (bf16 embed)
+        if fp8_dw:
+            g8 = cast_e4m3_sat(g.to(torch.float32) * 256.0).to(torch.float32)
+            acc = (g8 @ x8.to(torch.float32)) / 256.0
+        else:
+            acc = matmul_acc(g, x32)                           # fuse_kernel.py:84-96 (bf16 embed)
         first = lo * d
         sd = seed
         tri = rounding == 'sr_triton'

@@ -34,8 +34,9 @@ def run_check(dev, rank, world):
     eng = CudaShardEngine(dev, d, b_loc * world, "fp8", lo, mine, sched_labels=512)
     layer = LabelShardedXMC(eng, dim=d, local_batch=b_loc, num_rows=L, label_capacity=256, device=dev,
                             base_seed=77, rounding="sr")
-    for it in range(2):
-        layer.xfc_forward_backward(xs[rank].to(dev), labs[rank].to(dev), [0.4])
+    layer.xfc_forward_backward(xs[rank].to(dev), labs[rank].to(dev), [0.4])
+    layer.prefetch_labels(labs[rank].to(dev))                   # second step: labels gathered on the side stream
+    layer.xfc_forward_backward(xs[rank].to(dev), None, [0.4])
     tv, ti = layer.xfc_topk(xs[rank].to(dev), k, L - 5)
     eng.handle.check()
 

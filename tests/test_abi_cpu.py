@@ -51,7 +51,10 @@ def test_no_cpu_fallback():
     for cls in (Fp8XMCBCEChunkedLayer, XMCBCECHUNKEDLayer):
         with pytest.raises(RuntimeError, match="CUDA"):
             cls(cfg)
-    cfg.model.xmc.dtype = "float32"
+    cfg.model.xmc.dtype = "float32"                                # the torch-statement path refuses a CPU device too
+    with pytest.raises(RuntimeError, match="CUDA"):
+        XMCBCECHUNKEDLayer(cfg)
+    cfg.model.xmc.dtype = "float8"
     with pytest.raises(NotImplementedError):
         XMCBCECHUNKEDLayer(cfg)
 

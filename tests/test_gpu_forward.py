@@ -155,3 +155,30 @@ def test_sigmoid_of_every_bf16_input():
     # flush-to-zero of the approximate ops may turn a result below 2^-126 into 0: allow those
     tiny = want.float().abs()[ok] < 2.0 ** -120
     assert bool((same | tiny).all()), int((~(same | tiny)).sum())
+
+
+@pytest.mark.parametrize("dtype_name", ["float32", "float16"])
+def test_chunked_layer_float_weights_match_reference_fixture(dtype_name):
+    """float32 / float16 weights of XMCBCECHUNKEDLayer (plain torch statements, as in the reference)
+    against the fixture the unmodified reference produced in float32 (tests/golden/chunked_fp32.npz)."""
+    from types import SimpleNamespace as NS
+    from elmo_b200.xmc_classifiers import XMCBCECHUNKEDLayer
+    from tests._util import load_golden, rel_inf
+    g = load_golden("chunked_fp32.npz")
+    L, d, B, nc, lr = int(g["L"]), int(g["d"]), int(g["B"]), int(g["nc"]), float(g["lr"])
+    cfg = NS(environment=NS(device="cuda:0"),
+             model=NS(xmc=NS(dtype=dtype_name, num_chunks=nc, input_features=d)),
+             training=NS(precision=NS(mode="mixed", purelp_dtype="bfloat16"), xmc=NS(momentum=0, wd=0.0, simulated_fp8=False)),
+             data=NS(num_labels=L, batch_size=B))
+    layer = XMCBCECHUNKEDLayer(cfg)
+    layer.xfc_weight.copy_(torch.from_numpy(g["w0"]).to(layer._dtype))
+    tol = 1e-5 if dtype_name == "float32" else 2e-2
+    for s in range(2):
+        x = torch.from_numpy(g[f"x{s}"]).cuda()
+        lab = torch.from_numpy(g[f"labels{s}"]).cuda()
+        loss = layer.xfc_forward_backward(x, lab, [lr], skip_loss=(s == 0))
+        assert rel_inf(layer.xfc_weight.float().cpu(), torch.from_numpy(g[f"w{s + 1}"])) < tol
+        assert rel_inf(layer.grad_input.float().cpu(), torch.from_numpy(g[f"grad_input{s}"])) < max(tol, 1e-4)
+    assert loss > 0 and layer.iteration == 2
+    z = layer.xfc_forward(torch.from_numpy(g["x1"]).cuda())
+    assert rel_inf(z.float().cpu(), torch.from_numpy(g["logits_last"])) < max(tol, 1e-4)

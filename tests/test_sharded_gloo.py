@@ -52,8 +52,9 @@ def _worker(rank, port, out):
         mine = [w[lo:hi].clone()]
         layer = LabelShardedXMC(OracleEngine(mine, lo), dim=D, local_batch=B_LOC, num_rows=L,
                                 label_capacity=16, base_seed=9, rounding="sr")
-        for it in range(2):
-            layer.xfc_forward_backward(xs[rank], labs[rank], [0.5])
+        layer.xfc_forward_backward(xs[rank], labs[rank], [0.5])
+        layer.prefetch_labels(labs[rank])                       # second step: labels gathered ahead of the "encoder"
+        layer.xfc_forward_backward(xs[rank], None, [0.5])
         tv, ti = layer.xfc_topk(xs[rank], 4, L - 7)
         # checkpoint: per-rank state with its shard map, and the gathered reference layout (3 chunks)
         sd = layer.state_dict()
