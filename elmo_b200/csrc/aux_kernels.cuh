@@ -195,23 +195,6 @@ bucket_all_kernel(const int32_t* __restrict__ labels, int nnz, int batch, Bucket
   }
 }
 
-// e4m3 -> bf16 staging of one scheduling chunk of weights (exact); n16 = number of 16-byte groups
-__global__ void e4m3_to_bf16_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long long n16) {
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += stride) {
-    const uint4 raw = src[i];
-    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-    uint32_t o[8];
-#pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const float2 f = e4m3x2_to_float2((uint16_t)(w[k >> 1] >> (16 * (k & 1))));
-      o[k] = pack_bf16x2(f.x, f.y);
-    }
-    dst[2 * i] = make_uint4(o[0], o[1], o[2], o[3]);
-    dst[2 * i + 1] = make_uint4(o[4], o[5], o[6], o[7]);
-  }
-}
-
 // Scale bookkeeping: one streaming pass over e4m3 weights (n16 groups of 16 bytes).
 // counts[0] zeros, [1] sub-normal magnitudes (0 < |w| < 2^-6), [2] at +-448, [3] NaN; amax_bits = largest
 // magnitude byte seen (e4m3 magnitudes order like their bytes).

@@ -10,6 +10,9 @@
 // epilogue of tile t overlaps the main loop of tile t+1.  Every wait is bounded (ptx.cuh).
 //
 // A policy supplies: operand kind/majorness, the tile -> job mapping and the epilogue.  A policy with
+// kConv = 1 (2) takes its A (B) operand from e4m3 storage although it multiplies in bf16 (the
+// "simulated FP8" arithmetic): the producer brings the raw bytes in, four extra warps rewrite them as
+// bf16 in the operand's swizzled layout, and the MMA issuer waits for both.  A policy with
 // kCTile set also has the producer fetch, per tile, the 128 x 256-byte block of a third tensor (the
 // weights the update epilogue reads and rewrites) into a two-deep shared-memory ring while the tile's
 // main loop runs; the epilogue rewrites the block in place and one TMA store writes it back, so no
@@ -56,6 +59,8 @@ struct SharedTail {
   uint64_t empty[kMaxStages];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
+  uint64_t raw_full[kMaxStages];   // kConv policies: the raw e4m3 bytes of the stage have landed
+  uint64_t conv_full[kMaxStages];  // ... and have been rewritten as bf16 (one arrival per converter warp)
   uint64_t c_full[2];      // epilogue tile landed (kCTile policies)
   uint64_t c_done[2];      // all epilogue warps have rewritten their part of it
   uint64_t c_empty[2];     // it has been stored back and may be refilled
@@ -63,11 +68,16 @@ struct SharedTail {
   Ctl ctl;
 };
 constexpr int kBitmapBytes = kTileM * (kTileN / 32) * 4;
+constexpr int kConvWarps = 4;
+template <class Policy>
+__host__ __device__ constexpr int conv_rows() { return Policy::kConv == 1 ? kTileM : (Policy::kConv == 2 ? kTileN : 0); }
+template <class Policy>
+__host__ __device__ constexpr int block_threads() { return 64 + 32 * Policy::kEpiWarps + (Policy::kConv ? 32 * kConvWarps : 0); }
 
 
 template <class Policy>
 __host__ __device__ constexpr int smem_bytes() {
-  return Policy::kStages * kStageBytes + (Policy::kCTile ? Policy::kCBufs * kCTileBytes : 0) +
+  return Policy::kStages * (kStageBytes + conv_rows<Policy>() * 64) + (Policy::kCTile ? Policy::kCBufs * kCTileBytes : 0) +
          (Policy::kBitmap ? kBitmapBytes : 0) + (int)sizeof(SharedTail) + 1024;
 }
 
@@ -79,7 +89,7 @@ __device__ __forceinline__ uint2* ctile_ptr8(uint8_t* tile, int row, int col) {
 }
 
 template <class Policy>
-__global__ void __launch_bounds__(64 + 32 * Policy::kEpiWarps, 1)
+__global__ void __launch_bounds__(block_threads<Policy>(), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
             const __grid_constant__ CUtensorMap map_c, const typename Policy::Params p) {
   constexpr int kStages = Policy::kStages;
@@ -88,7 +98,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the 128-byte swizzle pattern is a function of address bits [4,10)
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint8_t* smem_c = smem + kStages * kStageBytes;
+  constexpr int kRawBytes = conv_rows<Policy>() * 64;      // raw e4m3 bytes of one k-step of the converted operand
+  uint8_t* smem_raw_ring = smem + kStages * kStageBytes;
+  uint8_t* smem_c = smem_raw_ring + kStages * kRawBytes;
   uint8_t* smem_bm = smem_c + (Policy::kCTile ? Policy::kCBufs * kCTileBytes : 0);
   SharedTail& sh = *reinterpret_cast<SharedTail*>(smem_bm + (Policy::kBitmap ? kBitmapBytes : 0));
   constexpr uint32_t kCBufs = Policy::kCTile ? (uint32_t)Policy::kCBufs : 1u;
@@ -100,6 +112,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     for (int s = 0; s < kStages; ++s) {
       mbar_init(smem_u32(&sh.full[s]), 1);
       mbar_init(smem_u32(&sh.empty[s]), 1);
+      mbar_init(smem_u32(&sh.raw_full[s]), 1);
+      mbar_init(smem_u32(&sh.conv_full[s]), kConvWarps);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&sh.tmem_full[b]), 1);
@@ -171,9 +185,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           const uint32_t sb = sa + kStageABytes;
           if constexpr (!Policy::kMnMajor) {
             if (!Policy::skip_load(p, tile, k) && elect_one()) {
-              mbar_arrive_expect_tx(bar, kStageBytes);
-              tma_load_2d(sa, &map_a, bar, kk, job.a0);
-              tma_load_2d(sb, &map_b, bar, kk, job.b0);
+              if constexpr (Policy::kConv == 0) {
+                mbar_arrive_expect_tx(bar, kStageBytes);
+                tma_load_2d(sa, &map_a, bar, kk, job.a0);
+                tma_load_2d(sb, &map_b, bar, kk, job.b0);
+              } else {
+                // the converted operand arrives raw (64 bytes per row = the 64 bf16 elements of this k-step)
+                const uint32_t rbar = smem_u32(&sh.raw_full[s]);
+                const uint32_t raw = smem_u32(smem_raw_ring + s * kRawBytes);
+                mbar_arrive_expect_tx(rbar, kRawBytes);
+                if constexpr (Policy::kConv == 1) {
+                  tma_load_2d(raw, &map_a, rbar, kk, job.a0);
+                  mbar_arrive_expect_tx(bar, kStageBBytes);
+                  tma_load_2d(sb, &map_b, bar, kk, job.b0);
+                } else {
+                  tma_load_2d(raw, &map_b, rbar, kk, job.b0);
+                  mbar_arrive_expect_tx(bar, kStageABytes);
+                  tma_load_2d(sa, &map_a, bar, kk, job.a0);
+                }
+              }
             }
             kk += Policy::kElemsPerRow;
           } else {
@@ -229,6 +259,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             ok = false;
             break;
           }
+          if constexpr (Policy::kConv != 0) {
+            if (!mbar_wait_warp(smem_u32(&sh.conv_full[s]), ph, &sh.ctl, p.status, 310 + (int)s)) {
+              ok = false;
+              break;
+            }
+          }
           tc_fence_after();
           const uint32_t a_lo = a_lo0 + s * (uint32_t)(kStageBytes >> 4);
           const uint32_t b_lo = a_lo + (uint32_t)(kStageABytes >> 4);
@@ -249,6 +285,51 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         }
         if (ok && elect_one()) umma_commit(smem_u32(&sh.tmem_full[buf]));
         __syncwarp();
+      }
+    }
+  } else if (Policy::kConv != 0 && warp >= 2 + Policy::kEpiWarps) {
+    // ------------------------------ operand converters ------------------------------
+    // 128 threads rewrite the stage's raw e4m3 rows as bf16 in the K-major 128-byte-swizzled operand
+    // layout (row r at r * 128, 16-byte piece c at c ^ (r & 7)).  Thread t takes (row, quarter) pairs
+    // t, t + 128, ...: reads are consecutive 16-byte pieces, the two pieces written per pair of adjacent
+    // rows cover all eight positions, so neither side has bank conflicts.  The raw bytes land only after
+    // the producer has seen the stage released, so nothing else has to be waited for.
+    if constexpr (Policy::kConv != 0) {
+      const int ct = threadIdx.x - 32 * (2 + Policy::kEpiWarps);
+      uint32_t s = 0, ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+        Job job;
+        Policy::job(p, tile, job);
+        for (int k = 0; k < job.k_steps; ++k) {
+          if (!mbar_wait(smem_u32(&sh.raw_full[s]), ph, &sh.ctl, p.status, 700 + (int)s)) {
+            ok = false;
+            break;
+          }
+          const uint8_t* raw = smem_raw_ring + s * kRawBytes;
+          uint8_t* dst = smem + s * kStageBytes + (Policy::kConv == 2 ? kStageABytes : 0);
+#pragma unroll
+          for (int it = 0; it < conv_rows<Policy>() * 4 / (32 * kConvWarps); ++it) {
+            const int pr = ct + it * 32 * kConvWarps;
+            const int row = pr >> 2, kc = pr & 3;
+            const uint4 v = *reinterpret_cast<const uint4*>(raw + row * 64 + kc * 16);
+            uint4 o0, o1;
+            e4m3x4_to_bf16x4(v.x, o0.x, o0.y);
+            e4m3x4_to_bf16x4(v.y, o0.z, o0.w);
+            e4m3x4_to_bf16x4(v.z, o1.x, o1.y);
+            e4m3x4_to_bf16x4(v.w, o1.z, o1.w);
+            uint8_t* rowp = dst + row * 128;
+            *reinterpret_cast<uint4*>(rowp + (((2 * kc) ^ (row & 7)) << 4)) = o0;
+            *reinterpret_cast<uint4*>(rowp + (((2 * kc + 1) ^ (row & 7)) << 4)) = o1;
+          }
+          fence_proxy_async();                            // generic-proxy writes -> tensor-core reads
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&sh.conv_full[s]));
+          if (++s == (uint32_t)kStages) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
       }
     }
   } else {

@@ -85,4 +85,17 @@ __device__ __forceinline__ uint32_t sr_bf16_bits(float w, uint32_t r16) {
   return (__float_as_uint(w) + r16) >> 16;
 }
 
+// four e4m3 bytes -> four bf16 (two packed words), exact, integer/FMA pipes only.
+// (b & 0x7f) << 4 placed in a bf16 is the value times 2^-120, subnormals included; one packed
+// multiply by 2^120 restores it.
+__device__ __forceinline__ void e4m3x4_to_bf16x4(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  const uint32_t t0 = __byte_perm(w, 0u, 0x1404);     // b1 << 24 | b0 << 8
+  const uint32_t t1 = __byte_perm(w, 0u, 0x3424);     // b3 << 24 | b2 << 8
+  const uint32_t x0 = (t0 & 0x80008000u) | ((t0 >> 4) & 0x07F007F0u);
+  const uint32_t x1 = (t1 & 0x80008000u) | ((t1 >> 4) & 0x07F007F0u);
+  const uint32_t scale = 0x7B807B80u;                 // bf16x2 (2^120, 2^120)
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(lo) : "r"(x0), "r"(scale));
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(hi) : "r"(x1), "r"(scale));
+}
+
 }  // namespace xmc

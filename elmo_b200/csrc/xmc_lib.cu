@@ -153,6 +153,12 @@ int make_map_kmajor(CUtensorMap* m, bool e4m3, const void* base, uint64_t k_elem
   const uint32_t es = e4m3 ? 1 : 2;
   return make_map(m, e4m3, base, k_elems, rows, row_stride_elems * es, 128 / es, box_rows);
 }
+// e4m3 rows [rows x k_bytes] fetched raw, 64 bytes (one bf16 k-step) of `box_rows` rows per box, for the
+// in-kernel conversion to a bf16 operand
+int make_map_raw8(CUtensorMap* m, const void* base, uint64_t k_bytes, uint64_t rows, uint64_t row_stride_bytes,
+                  uint32_t box_rows) {
+  return make_map(m, true, base, k_bytes, rows, row_stride_bytes, 64, box_rows, false);
+}
 // bf16 operand stored [k_rows x mn] (MN contiguous): boxes of box_rows k-rows x 64 elements
 int make_map_mnmajor(CUtensorMap* m, const void* base, uint64_t mn, uint64_t k_rows,
                      uint64_t row_stride_elems, uint32_t box_rows = 64) {
@@ -207,7 +213,7 @@ int launch_gemm(const CUtensorMap& a, const CUtensorMap& b, const typename Polic
   }
   if (Policy::kCTile && c == nullptr) return fail(XMC_ERR_STATE, "this kernel needs its epilogue-input tensor map");
   int grid = grid_override > 0 ? grid_override : std::min(n_tiles, sm_count);
-  CU_TRY(launch_pdl(kern, grid, 64 + 32 * Policy::kEpiWarps, smem, stream, a, b, c ? *c : a, p));
+  CU_TRY(launch_pdl(kern, grid, xmc::block_threads<Policy>(), smem, stream, a, b, c ? *c : a, p));
   return XMC_OK;
 }
 
@@ -222,7 +228,7 @@ struct xmc_handle {
   int bpad_max = 0;
   int sched = 0;                   // labels per scheduling chunk in use (set when the weights are bound)
   int sched_cfg = 0;               // the configured / automatic value
-  int64_t g_rows = 0;              // rows of G / w16 currently allocated
+  int64_t g_rows = 0;              // rows of G currently allocated
   std::vector<void*> w_ptrs;
   std::vector<int64_t> w_rows;
   int64_t total_rows = 0;
@@ -236,7 +242,6 @@ struct xmc_handle {
   uint8_t* G8 = nullptr;           // [sched x bpad_max] e4m3(G * 256), allocated when the FP8 dW contraction is first asked for
   uint8_t* xt8 = nullptr;          // [max(d,256) x bpad_max] e4m3 X transposed, likewise
   int64_t g8_rows = 0;
-  __nv_bfloat16* w16 = nullptr;    // [sched x d] bf16 staging of an e4m3 chunk
   float* partial = nullptr;
   int64_t partial_floats = 0;
   int* bucket_cnt = nullptr;       // [2 * n_buckets] counts then cursors
@@ -405,7 +410,7 @@ int xmc_destroy(xmc_handle* h) {
   if (h == nullptr) return XMC_OK;
   DeviceGuard guard(h->cfg.device);
   if (h->l2_persist_bytes > 0) cudaCtxResetPersistingL2Cache();   // lines pinned for the partial sums become normal again
-  void* ptrs[] = {h->x8, h->x16, h->xt, h->G, h->G8, h->xt8, h->w16, h->partial, h->bucket_cnt, h->bucket_off,
+  void* ptrs[] = {h->x8, h->x16, h->xt, h->G, h->G8, h->xt8, h->partial, h->bucket_cnt, h->bucket_off,
                   h->entries, h->loss_partial, h->status, h->stats, h->topk_val, h->topk_idx, h->topk_cnt, h->topk_thr, h->topk_max, h->topk_row};
   for (void* p : ptrs)
     if (p != nullptr) cudaFree(p);
@@ -440,15 +445,10 @@ int xmc_bind_weights(xmc_handle* h, int32_t n_chunks, void* const* ptrs, const i
     h->sched = (int)round_up(rows[0], 128);
   const int64_t g_rows = std::min<int64_t>(h->sched, round_up(h->rows_per_chunk, 128));
   if (g_rows > h->g_rows) {
-    const int d = h->cfg.dim;
     if (h->G) { cudaFree(h->G); h->ws_bytes -= h->g_rows * h->bpad_max * 2; h->G = nullptr; }
     if (h->G8) { cudaFree(h->G8); h->ws_bytes -= h->g8_rows * h->bpad_max; h->G8 = nullptr; h->g8_rows = 0; }
-    if (h->w16) { cudaFree(h->w16); h->ws_bytes -= h->g_rows * d * 2; h->w16 = nullptr; }
     h->g_rows = 0;
     if (int rc = dev_alloc(h, (void**)&h->G, (size_t)g_rows * h->bpad_max * 2, true)) return rc;
-    if (h->cfg.mode == XMC_MODE_SIMFP8) {
-      if (int rc = dev_alloc(h, (void**)&h->w16, (size_t)g_rows * d * 2, true)) return rc;
-    }
     h->g_rows = g_rows;
   }
   const int spc = cdiv(h->rows_per_chunk, h->sched);
@@ -685,24 +685,16 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
       const size_t esz = w8 ? 1 : 2;
       uint8_t* wbase = reinterpret_cast<uint8_t*>(h->w_ptrs[wc]) + (size_t)s0 * d * esz;
 
-      // bf16 view of the chunk's weights for the bf16 contractions
-      const __nv_bfloat16* w16 = reinterpret_cast<const __nv_bfloat16*>(wbase);
-      if (mode == XMC_MODE_SIMFP8) {   // only the simulated-FP8 forward needs a bf16 copy of the chunk
-        const long long n16 = (long long)rows_valid * d / 16;
-        const int blocks = (int)std::min<long long>((n16 + 255) / 256, (long long)h->sm_count * 8);
-        mark(h, K_CONVERT, st);
-        xmc::e4m3_to_bf16_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const uint4*>(wbase),
-                                                         reinterpret_cast<uint4*>(h->w16), n16);
-        CU_TRY(cudaGetLastError());
-        w16 = h->w16;
-      }
-
       // forward + loss gradient -> G
       CUtensorMap map_w;
+      const bool sim = mode == XMC_MODE_SIMFP8;
       if (fwd_fp8) {
         if (int rc = make_map_kmajor(&map_w, true, wbase, d, rows_valid, d, 128)) return rc;
+      } else if (sim) {
+        // e4m3 storage, bf16 arithmetic: the kernel converts the weight operand in shared memory
+        if (int rc = make_map_raw8(&map_w, wbase, d, rows_valid, d, 128)) return rc;
       } else {
-        if (int rc = make_map_kmajor(&map_w, false, w16, d, rows_valid, d, 128)) return rc;
+        if (int rc = make_map_kmajor(&map_w, false, wbase, d, rows_valid, d, 128)) return rc;
       }
       xmc::FwdParams fp;
       fp.m_rows = 128;
@@ -731,6 +723,8 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
                               : launch_gemm<xmc::FwdPolicy<true, false, true>>(map_w, map_x, fp, f_tiles, h->sm_count, st);
       else if (fwd_fp8) rc = want_loss ? launch_gemm<xmc::FwdPolicy<true, true>>(map_w, map_x, fp, f_tiles, h->sm_count, st)
                                        : launch_gemm<xmc::FwdPolicy<true, false>>(map_w, map_x, fp, f_tiles, h->sm_count, st);
+      else if (sim) rc = want_loss ? launch_gemm<xmc::FwdPolicy<false, true, false, true>>(map_w, map_x, fp, f_tiles, h->sm_count, st)
+                                   : launch_gemm<xmc::FwdPolicy<false, false, false, true>>(map_w, map_x, fp, f_tiles, h->sm_count, st);
       else rc = want_loss ? launch_gemm<xmc::FwdPolicy<false, true>>(map_w, map_x, fp, f_tiles, h->sm_count, st)
                           : launch_gemm<xmc::FwdPolicy<false, false>>(map_w, map_x, fp, f_tiles, h->sm_count, st);
       if (rc) return rc;
@@ -903,18 +897,13 @@ int xmc_forward_logits(xmc_handle* h, const void* x, int32_t x_dtype, int32_t ba
       const int rows = (int)std::min<int64_t>(h->sched, rows_wc - s0);
       const size_t esz = mode == XMC_MODE_BF16 ? 2 : 1;
       const uint8_t* wbase = reinterpret_cast<const uint8_t*>(h->w_ptrs[wc]) + (size_t)s0 * d * esz;
-      const void* wsrc = wbase;
-      if (mode == XMC_MODE_SIMFP8) {
-        const long long n16 = (long long)rows * d / 16;
-        const int blocks = (int)std::min<long long>((n16 + 255) / 256, (long long)h->sm_count * 8);
-        mark(h, K_CONVERT, st);
-        xmc::e4m3_to_bf16_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const uint4*>(wbase),
-                                                         reinterpret_cast<uint4*>(h->w16), n16);
-        CU_TRY(cudaGetLastError());
-        wsrc = h->w16;
-      }
+      const bool sim = mode == XMC_MODE_SIMFP8;
       CUtensorMap map_w;
-      if (int rc = make_map_kmajor(&map_w, fwd_fp8, wsrc, d, rows, d, 256)) return rc;
+      if (sim) {
+        if (int rc = make_map_raw8(&map_w, wbase, d, rows, d, 256)) return rc;
+      } else {
+        if (int rc = make_map_kmajor(&map_w, fwd_fp8, wbase, d, rows, d, 256)) return rc;
+      }
       xmc::LogitsParams lp;
       lp.batch = batch;
       lp.rows = rows;
@@ -930,6 +919,7 @@ int xmc_forward_logits(xmc_handle* h, const void* x, int32_t x_dtype, int32_t ba
       mark(h, K_LOGITS, st);
       const int tiles = lp.n_mtiles * lp.n_ntiles;
       const int rc = fwd_fp8 ? launch_gemm<xmc::LogitsPolicy<true>>(map_x, map_w, lp, tiles, h->sm_count, st)
+                     : sim   ? launch_gemm<xmc::LogitsPolicy<false, true>>(map_x, map_w, lp, tiles, h->sm_count, st)
                              : launch_gemm<xmc::LogitsPolicy<false>>(map_x, map_w, lp, tiles, h->sm_count, st);
       if (rc) return rc;
     }
@@ -1006,16 +996,7 @@ int xmc_forward_topk(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batc
       const int rows = (int)std::min<int64_t>(h->sched, rows_wc - s0);
       const size_t esz = mode == XMC_MODE_BF16 ? 2 : 1;
       const uint8_t* wbase = reinterpret_cast<const uint8_t*>(h->w_ptrs[wc]) + (size_t)s0 * d * esz;
-      const void* wsrc = wbase;
-      if (mode == XMC_MODE_SIMFP8) {
-        const long long n16 = (long long)rows * d / 16;
-        const int blocks = (int)std::min<long long>((n16 + 255) / 256, (long long)h->sm_count * 8);
-        mark(h, K_CONVERT, st);
-        xmc::e4m3_to_bf16_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const uint4*>(wbase),
-                                                         reinterpret_cast<uint4*>(h->w16), n16);
-        CU_TRY(cudaGetLastError());
-        wsrc = h->w16;
-      }
+      const bool sim = mode == XMC_MODE_SIMFP8;
       // Mid-course thresholds: for k > 8 (the in-kernel k-th-of-maxima bound covers smaller k) the exact
       // k-th best value of what the lists hold is published after launches 1, 2, 4, 8, ...; the first one
       // turns the flood of the first launch (every logit is a candidate while nothing is known) into a
@@ -1028,7 +1009,11 @@ int xmc_forward_topk(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batc
         CU_TRY(cudaGetLastError());
       }
       CUtensorMap map_w;
-      if (int rc = make_map_kmajor(&map_w, fwd_fp8, wsrc, d, rows, d, 256)) return rc;
+      if (sim) {
+        if (int rc = make_map_raw8(&map_w, wbase, d, rows, d, 256)) return rc;
+      } else {
+        if (int rc = make_map_kmajor(&map_w, fwd_fp8, wbase, d, rows, d, 256)) return rc;
+      }
       xmc::TopkParams tp;
       tp.batch = batch;
       tp.rows = rows;
@@ -1054,6 +1039,7 @@ int xmc_forward_topk(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batc
       mark(h, K_LOGITS, st);
       int rc;
       rc = fwd_fp8 ? launch_gemm<xmc::TopkPolicy<true>>(map_x, map_w, tp, tiles, h->sm_count, st, grid)
+           : sim   ? launch_gemm<xmc::TopkPolicy<false, true>>(map_x, map_w, tp, tiles, h->sm_count, st, grid)
                    : launch_gemm<xmc::TopkPolicy<false>>(map_x, map_w, tp, tiles, h->sm_count, st, grid);
       if (rc) return rc;
       ++launch;

@@ -37,17 +37,21 @@ struct FwdParams {
 
 constexpr float kG8Scale = 256.0f;      // |G| < 1: e4m3(G * 256) stays below 448
 
-template <bool FP8, bool LOSS, bool WRITE_G8 = false>
+// CONV: bf16 arithmetic on e4m3-stored weights ("simulated FP8"): the weight operand (A) is converted in
+// shared memory by the engine's converter warps.
+template <bool FP8, bool LOSS, bool WRITE_G8 = false, bool CONV = false>
 struct FwdPolicy {
+  static_assert(!(FP8 && CONV), "the FP8 contraction takes the e4m3 weights as they are");
   using Params = FwdParams;
   static constexpr bool kMnMajor = false;
   static constexpr bool kFp8 = FP8;
   static constexpr uint32_t kFmt = FP8 ? 0u : 1u;            // e4m3 | bf16
   static constexpr int kElemsPerRow = FP8 ? 128 : 64;
   static constexpr int kEpiWarps = 8;
-  static constexpr int kStages = 4;
+  static constexpr int kStages = CONV ? 3 : 4;
   static constexpr bool kCTile = false;
   static constexpr int kCBufs = 1;
+  static constexpr int kConv = CONV ? 1 : 0;
   static constexpr bool kBitmap = true;
   __device__ static long long wait_limit(const Params&) { return kWaitLimitCycles; }
   __device__ static bool skip_load(const Params&, int, int) { return false; }
@@ -229,6 +233,7 @@ struct UpdPolicy {
   // (64 KB per tile) are read from and written to global memory by the epilogue threads
   static constexpr bool kCTile = W8;
   static constexpr int kCBufs = 2;
+  static constexpr int kConv = 0;
   static constexpr bool kBitmap = false;
   __device__ static long long wait_limit(const Params&) { return kWaitLimitCycles; }
   __device__ static bool skip_load(const Params&, int, int) { return false; }
@@ -515,17 +520,19 @@ struct LogitsParams {
   int* status;
 };
 
-template <bool FP8>
+template <bool FP8, bool CONV = false>
 struct LogitsPolicy {
+  static_assert(!(FP8 && CONV), "the FP8 contraction takes the e4m3 weights as they are");
   using Params = LogitsParams;
   static constexpr bool kMnMajor = false;
   static constexpr bool kFp8 = FP8;
   static constexpr uint32_t kFmt = FP8 ? 0u : 1u;
   static constexpr int kElemsPerRow = FP8 ? 128 : 64;
   static constexpr int kEpiWarps = 8;
-  static constexpr int kStages = 4;
+  static constexpr int kStages = CONV ? 3 : 4;
   static constexpr bool kCTile = false;
   static constexpr int kCBufs = 1;
+  static constexpr int kConv = CONV ? 2 : 0;      // the weights are the B operand here
   static constexpr bool kBitmap = false;
   __device__ static long long wait_limit(const Params&) { return kWaitLimitCycles; }
   __device__ static bool skip_load(const Params&, int, int) { return false; }
@@ -623,17 +630,19 @@ __device__ __forceinline__ float topk_unkey(unsigned int k) {
 // its k best by a radix select, which raises both thresholds.  Appending is a few instructions, so the
 // divergence of 32 lanes with 32 different rows stays cheap, and because all lists of a row share the
 // published threshold the number of candidates per row stays near k ln(L/k) however many CTAs there are.
-template <bool FP8>
+template <bool FP8, bool CONV = false>
 struct TopkPolicy {
+  static_assert(!(FP8 && CONV), "the FP8 contraction takes the e4m3 weights as they are");
   using Params = TopkParams;
   static constexpr bool kMnMajor = false;
   static constexpr bool kFp8 = FP8;
   static constexpr uint32_t kFmt = FP8 ? 0u : 1u;
   static constexpr int kElemsPerRow = FP8 ? 128 : 64;
   static constexpr int kEpiWarps = 8;
-  static constexpr int kStages = 4;
+  static constexpr int kStages = CONV ? 3 : 4;
   static constexpr bool kCTile = false;
   static constexpr int kCBufs = 1;
+  static constexpr int kConv = CONV ? 2 : 0;
   static constexpr bool kBitmap = false;
   __device__ static long long wait_limit(const Params&) { return kWaitLimitCycles; }
   __device__ static bool skip_load(const Params&, int, int) { return false; }
@@ -871,6 +880,7 @@ struct PlainPolicy {
   static constexpr int kStages = 4;
   static constexpr bool kCTile = false;
   static constexpr int kCBufs = 1;
+  static constexpr int kConv = 0;
   static constexpr bool kBitmap = false;
   // failure-injection of the self-test: a shortened wait limit and one operand load left out
   __device__ static long long wait_limit(const Params& p) { return p.test_wait_limit > 0 ? p.test_wait_limit : kWaitLimitCycles; }
