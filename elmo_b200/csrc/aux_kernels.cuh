@@ -341,12 +341,15 @@ topk_select_kernel(const float* __restrict__ cand_val, const int* __restrict__ c
       if (((sl + 2) & 3) == q) slot = sl;
     return (c * 8 + slot) * 32 + lane;
   };
-  // visit every candidate at or above the published threshold, from the lists in global memory
+  // visit every candidate at or above the published threshold, from the lists in global memory: a warp
+  // per list, lanes along the list (coalesced)
   auto for_each_global = [&](auto&& f) {
-    for (int r = threadIdx.x; r < lists; r += blockDim.x) {
-      const size_t base = (size_t)list_of(r) * (cap + 32);
-      const int n = list_cnt[list_of(r)];
-      for (int e = 0; e < n; ++e) {
+    const int wid = threadIdx.x >> 5, ln = threadIdx.x & 31, nw = blockDim.x >> 5;
+    for (int r = wid; r < lists; r += nw) {
+      const int li = list_of(r);
+      const size_t base = (size_t)li * (cap + 32);
+      const int n = list_cnt[li];
+      for (int e = ln; e < n; e += 32) {
         const float v = cand_val[base + e];
         if (v >= g) f(topk_key64(v, cand_idx[base + e]));
       }

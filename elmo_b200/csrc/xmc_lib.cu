@@ -992,8 +992,14 @@ int xmc_forward_topk(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batc
   int64_t row_base = 0;
   for (size_t wc = 0; wc < h->w_ptrs.size() && row_base < n_out; ++wc) {
     const int64_t rows_wc = h->w_rows[wc];
-    for (int64_t s0 = 0; s0 < rows_wc && row_base + s0 < n_out; s0 += h->sched) {
-      const int rows = (int)std::min<int64_t>(h->sched, rows_wc - s0);
+    int64_t s_next = 0;
+    for (int64_t s0 = 0; s0 < rows_wc && row_base + s0 < n_out; s0 = s_next) {
+      int rows = (int)std::min<int64_t>(h->sched, rows_wc - s0);
+      // While nothing is known every logit is a candidate: for k > 8 the very first launch therefore covers
+      // only 8192 label rows (few enough that no list fills up), and the threshold pass that follows it
+      // gives the rest of the call a bound to prune against.
+      if (k > 8 && launch == 0) rows = std::min(rows, 8192);
+      s_next = s0 + rows;
       const size_t esz = mode == XMC_MODE_BF16 ? 2 : 1;
       const uint8_t* wbase = reinterpret_cast<const uint8_t*>(h->w_ptrs[wc]) + (size_t)s0 * d * esz;
       const bool sim = mode == XMC_MODE_SIMFP8;
