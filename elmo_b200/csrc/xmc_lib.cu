@@ -167,20 +167,36 @@ int make_map_mnmajor(CUtensorMap* m, const void* base, uint64_t mn, uint64_t k_r
 
 // Launch with programmatic stream serialization: the kernel may be scheduled while its predecessor in
 // the stream drains; it orders itself with griddepcontrol.wait before its first global access.
+// cluster > 1 launches thread-block clusters of that many CTAs along x.
+inline void launch_config(cudaLaunchConfig_t* cfg, cudaLaunchAttribute* at, int grid, int block, size_t smem,
+                          cudaStream_t stream, int cluster) {
+  memset(cfg, 0, sizeof(*cfg));
+  cfg->gridDim = dim3((unsigned)grid);
+  cfg->blockDim = dim3((unsigned)block);
+  cfg->dynamicSmemBytes = smem;
+  cfg->stream = stream;
+  static const bool no_pdl = getenv("XMC_NO_PDL") != nullptr;
+  int n = 0;
+  if (!no_pdl) {
+    at[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster > 1) {
+    at[n].id = cudaLaunchAttributeClusterDimension;
+    at[n].val.clusterDim.x = (unsigned)cluster;
+    at[n].val.clusterDim.y = 1;
+    at[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  cfg->attrs = at;
+  cfg->numAttrs = n;
+}
 template <class Kern, class... Args>
 cudaError_t launch_pdl(Kern kern, int grid, int block, size_t smem, cudaStream_t stream, const Args&... args) {
   cudaLaunchConfig_t cfg;
-  memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3((unsigned)grid);
-  cfg.blockDim = dim3((unsigned)block);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = stream;
-  cudaLaunchAttribute at[1];
-  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  at[0].val.programmaticStreamSerializationAllowed = 1;
-  static const bool off = getenv("XMC_NO_PDL") != nullptr;
-  cfg.attrs = at;
-  cfg.numAttrs = off ? 0 : 1;
+  cudaLaunchAttribute at[2];
+  launch_config(&cfg, at, grid, block, smem, stream, 1);
   return cudaLaunchKernelEx(&cfg, kern, args...);
 }
 
@@ -197,23 +213,42 @@ int gradx_configure() {
   return XMC_OK;
 }
 
-template <class Policy>
+// PAIR: the kernel runs on CTA pairs (clusters of two); n_tiles then counts the pairs' 256-row tiles and
+// the grid is twice the number of pairs the device can hold at once (asked of the occupancy calculator:
+// an SM that has no partner within its GPC cannot take part).
+template <class Policy, bool PAIR = false>
 int launch_gemm(const CUtensorMap& a, const CUtensorMap& b, const typename Policy::Params& p, int n_tiles,
                 int sm_count, cudaStream_t stream, int grid_override = 0, const CUtensorMap* c = nullptr) {
   if (n_tiles <= 0) return XMC_OK;
-  auto kern = xmc::gemm_kernel<Policy>;
-  constexpr int smem = xmc::smem_bytes<Policy>();
+  auto kern = xmc::gemm_kernel<Policy, PAIR>;
+  constexpr int smem = xmc::smem_bytes<Policy, PAIR>();
+  constexpr int block = xmc::block_threads<Policy>();
   // once per device and kernel (one process may drive several devices)
   static std::atomic<uint64_t> configured{0};
+  static std::atomic<int> max_pairs[64];
   int dev = 0;
   CU_TRY(cudaGetDevice(&dev));
-  if (!((configured.load(std::memory_order_relaxed) >> (dev & 63)) & 1ull)) {
+  if (!((configured.load(std::memory_order_acquire) >> (dev & 63)) & 1ull)) {
     CU_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    configured.fetch_or(1ull << (dev & 63));
+    if (PAIR) {
+      cudaLaunchConfig_t cfg;
+      cudaLaunchAttribute at[2];
+      launch_config(&cfg, at, sm_count / 2 * 2, block, smem, stream, 2);
+      int n = 0;
+      CU_TRY(cudaOccupancyMaxActiveClusters(&n, kern, &cfg));
+      if (n <= 0) return fail(XMC_ERR_CUDA, "the device cannot hold a pair of CTAs of this kernel");
+      max_pairs[dev & 63].store(std::min(n, sm_count / 2), std::memory_order_relaxed);
+    }
+    configured.fetch_or(1ull << (dev & 63), std::memory_order_release);
   }
   if (Policy::kCTile && c == nullptr) return fail(XMC_ERR_STATE, "this kernel needs its epilogue-input tensor map");
-  int grid = grid_override > 0 ? grid_override : std::min(n_tiles, sm_count);
-  CU_TRY(launch_pdl(kern, grid, xmc::block_threads<Policy>(), smem, stream, a, b, c ? *c : a, p));
+  cudaLaunchConfig_t cfg;
+  cudaLaunchAttribute at[2];
+  int grid;
+  if (PAIR) grid = 2 * (grid_override > 0 ? grid_override : std::min(n_tiles, max_pairs[dev & 63].load(std::memory_order_relaxed)));
+  else grid = grid_override > 0 ? grid_override : std::min(n_tiles, sm_count);
+  launch_config(&cfg, at, grid, block, smem, stream, PAIR ? 2 : 1);
+  CU_TRY(cudaLaunchKernelEx(&cfg, kern, a, b, c ? *c : a, p));
   return XMC_OK;
 }
 
@@ -655,16 +690,21 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
   // --- operand maps that do not change across chunks ---
   CUtensorMap map_x, map_xt, map_g_k, map_g_mn;
   const size_t xrows = (size_t)std::max(h->bpad_max, 256);
+  // CTA pairs (256-row label tiles, each CTA staging half of the other operand's rows) for the kernels
+  // that take their operands as stored: the FP8 and bf16 forward, every update
+  static const bool no_pairs = getenv("XMC_NO_PAIRS") != nullptr;
+  const bool pair_fwd = !no_pairs && mode != XMC_MODE_SIMFP8;
+  const bool pair_upd = !no_pairs;
   if (fwd_fp8) {
-    if (int rc = make_map_kmajor(&map_x, true, h->x8, d, xrows, d, 256)) return rc;
+    if (int rc = make_map_kmajor(&map_x, true, h->x8, d, xrows, d, pair_fwd ? 128 : 256)) return rc;
   } else {
-    if (int rc = make_map_kmajor(&map_x, false, h->x16, d, xrows, d, 256)) return rc;
+    if (int rc = make_map_kmajor(&map_x, false, h->x16, d, xrows, d, pair_fwd ? 128 : 256)) return rc;
   }
   if (dw8) {
-    if (int rc = make_map_kmajor(&map_xt, true, h->xt8, bpad, std::max(d, 256), bpad, 256)) return rc;
+    if (int rc = make_map_kmajor(&map_xt, true, h->xt8, bpad, std::max(d, 256), bpad, pair_upd ? 128 : 256)) return rc;
     if (int rc = make_map_kmajor(&map_g_k, true, h->G8, bpad, h->g8_rows, bpad, 128)) return rc;
   } else {
-    if (int rc = make_map_kmajor(&map_xt, false, h->xt, bpad, std::max(d, 256), bpad, 256)) return rc;
+    if (int rc = make_map_kmajor(&map_xt, false, h->xt, bpad, std::max(d, 256), bpad, pair_upd ? 128 : 256)) return rc;
     if (int rc = make_map_kmajor(&map_g_k, false, h->G, bpad, h->g_rows, bpad, 128)) return rc;
   }
   if (int rc = make_map_blocked(&map_g_mn, false, h->G, bpad, h->g_rows, bpad, xmc::kGxRows, true)) return rc;
@@ -697,10 +737,11 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
         if (int rc = make_map_kmajor(&map_w, false, wbase, d, rows_valid, d, 128)) return rc;
       }
       xmc::FwdParams fp;
-      fp.m_rows = 128;
+      fp.m_rows = pair_fwd ? 256 : 128;
       fp.rows_valid = rows_valid;
-      fp.n_ltiles = n_lt;
+      fp.n_ltiles = cdiv(rows_valid, fp.m_rows);
       fp.n_btiles = cdiv(bpad, 256);
+      fp.div_btiles = xmc::make_fastdiv(fp.n_btiles);
       fp.batch = batch;
       fp.bpad = bpad;
       fp.k_steps = cdiv((long long)d * (fwd_fp8 ? 1 : 2), 128);
@@ -713,20 +754,20 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
       fp.loss_partial = want_loss ? h->loss_partial + (size_t)launch_idx * h->sm_count * xmc::kMaxEpiWarps : nullptr;
       fp.status = h->status;
       const int f_tiles = fp.n_ltiles * fp.n_btiles;
-      if (want_loss && std::min(f_tiles, h->sm_count) < h->sm_count) {
+      if (want_loss && (pair_fwd || f_tiles < h->sm_count)) {
         // slots of CTAs that are not launched must read as zero
         CU_TRY(cudaMemsetAsync(fp.loss_partial, 0, (size_t)h->sm_count * xmc::kMaxEpiWarps * sizeof(double), st));
       }
       int rc;
       mark(h, K_FWD, st);
-      if (dw8) rc = want_loss ? launch_gemm<xmc::FwdPolicy<true, true, true>>(map_w, map_x, fp, f_tiles, h->sm_count, st)
-                              : launch_gemm<xmc::FwdPolicy<true, false, true>>(map_w, map_x, fp, f_tiles, h->sm_count, st);
-      else if (fwd_fp8) rc = want_loss ? launch_gemm<xmc::FwdPolicy<true, true>>(map_w, map_x, fp, f_tiles, h->sm_count, st)
-                                       : launch_gemm<xmc::FwdPolicy<true, false>>(map_w, map_x, fp, f_tiles, h->sm_count, st);
-      else if (sim) rc = want_loss ? launch_gemm<xmc::FwdPolicy<false, true, false, true>>(map_w, map_x, fp, f_tiles, h->sm_count, st)
-                                   : launch_gemm<xmc::FwdPolicy<false, false, false, true>>(map_w, map_x, fp, f_tiles, h->sm_count, st);
-      else rc = want_loss ? launch_gemm<xmc::FwdPolicy<false, true>>(map_w, map_x, fp, f_tiles, h->sm_count, st)
-                          : launch_gemm<xmc::FwdPolicy<false, false>>(map_w, map_x, fp, f_tiles, h->sm_count, st);
+#define XMC_FWD(PAIR_, FP8_, G8_, CONV_) \
+  (want_loss ? launch_gemm<xmc::FwdPolicy<FP8_, true, G8_, CONV_>, PAIR_>(map_w, map_x, fp, f_tiles, h->sm_count, st) \
+             : launch_gemm<xmc::FwdPolicy<FP8_, false, G8_, CONV_>, PAIR_>(map_w, map_x, fp, f_tiles, h->sm_count, st))
+      if (sim) rc = XMC_FWD(false, false, false, true);
+      else if (dw8) rc = pair_fwd ? XMC_FWD(true, true, true, false) : XMC_FWD(false, true, true, false);
+      else if (fwd_fp8) rc = pair_fwd ? XMC_FWD(true, true, false, false) : XMC_FWD(false, true, false, false);
+      else rc = pair_fwd ? XMC_FWD(true, false, false, false) : XMC_FWD(false, false, false, false);
+#undef XMC_FWD
       if (rc) return rc;
 
       // grad_X partials: uses the pre-update weights (reference: chunked.py:116 precedes :119-127)
@@ -762,9 +803,11 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
 
       // fused dW + SGD update of the chunk, in place
       xmc::UpdParams up;
+      up.m_rows = pair_upd ? 256 : 128;
       up.rows_valid = rows_valid;
-      up.n_ltiles = n_lt;
+      up.n_ltiles = cdiv(rows_valid, up.m_rows);
       up.n_dtiles = n_dt;
+      up.div_dtiles = xmc::make_fastdiv(n_dt);
       up.d = d;
       up.k_steps = cdiv(bpad, dw8 ? 128 : 64);
       up.W = wbase;
@@ -779,7 +822,7 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
       up.elem0 = (unsigned long long)(h->cfg.label_offset + row_base + s0) * (unsigned long long)d;
       up.round_dw_bf16 = (flags & XMC_STEP_ROUND_DW_BF16) ? 1 : 0;
       up.status = h->status;
-      const int u_tiles = n_lt * n_dt;
+      const int u_tiles = up.n_ltiles * n_dt;
       mark(h, K_UPD, st);
       // the reference pairs: e4m3 weights (no dW rounding), bf16 weights (dW materialised in bf16);
       // weight decay is off in both, so only those combinations get the branch-free fast kernels
@@ -799,14 +842,13 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
         if (int rc2 = make_map(&map_wt, true, wbase, d, rows_valid, d, 128, 128)) return rc2;
       }
       const CUtensorMap* wt = w8 ? &map_wt : nullptr;
-#define XMC_UPD(W8_, SR_, RD_, WD_) \
-  launch_gemm<xmc::UpdPolicy<W8_, SR_, RD_, WD_>>(map_g_k, map_xt, up, u_tiles, h->sm_count, st, 0, wt)
+#define XMC_UPD(...) \
+  (pair_upd ? launch_gemm<xmc::UpdPolicy<__VA_ARGS__>, true>(map_g_k, map_xt, up, u_tiles, h->sm_count, st, 0, wt) \
+            : launch_gemm<xmc::UpdPolicy<__VA_ARGS__>, false>(map_g_k, map_xt, up, u_tiles, h->sm_count, st, 0, wt))
       if (dw8) {
-        rc = sr ? launch_gemm<xmc::UpdPolicy<true, true, false, false, false, true>>(map_g_k, map_xt, up, u_tiles, h->sm_count, st, 0, wt)
-                : launch_gemm<xmc::UpdPolicy<true, false, false, false, false, true>>(map_g_k, map_xt, up, u_tiles, h->sm_count, st, 0, wt);
+        rc = sr ? XMC_UPD(true, true, false, false, false, true) : XMC_UPD(true, false, false, false, false, true);
       } else if (kahan_here) {
-        rc = sr ? launch_gemm<xmc::UpdPolicy<true, true, false, false, true>>(map_g_k, map_xt, up, u_tiles, h->sm_count, st, 0, wt)
-                : launch_gemm<xmc::UpdPolicy<true, false, false, false, true>>(map_g_k, map_xt, up, u_tiles, h->sm_count, st, 0, wt);
+        rc = sr ? XMC_UPD(true, true, false, false, true) : XMC_UPD(true, false, false, false, true);
       } else if (w8) {
         if (!rdw && !has_wd) rc = sr ? XMC_UPD(true, true, false, false) : XMC_UPD(true, false, false, false);
         else if (!rdw) rc = sr ? XMC_UPD(true, true, false, true) : XMC_UPD(true, false, false, true);
@@ -1165,8 +1207,10 @@ int xmc_test_gemm(int32_t device, int32_t layout, int32_t dtype, int32_t M, int3
                   const void* A, const void* B, float* D, void* stream) {
   if (A == nullptr || B == nullptr || D == nullptr || M <= 0 || N <= 0 || K <= 0) return fail(XMC_ERR_INVALID, "bad argument");
   const bool inject = (layout & 8) != 0;
-  layout &= ~8;
-  if (layout < 0 || layout > 3) return fail(XMC_ERR_INVALID, "layout must be 0..3 (| 8)");
+  const bool pair = (layout & 4) != 0;
+  layout &= ~12;
+  if (layout < 0 || layout > 3) return fail(XMC_ERR_INVALID, "layout must be 0..3 (| 4 | 8)");
+  if (pair && (layout & 1) != 0) return fail(XMC_ERR_INVALID, "CTA pairs take K-major operands");
   if (inject && ((layout & 1) != 0 || K < 2 * (dtype == XMC_DT_E4M3 ? 128 : 64)))
     return fail(XMC_ERR_INVALID, "the wait-limit test takes K-major operands with at least two k-steps");
   if ((layout & 1) == 1 && dtype != XMC_DT_BF16) return fail(XMC_ERR_INVALID, "MN-major test takes bf16");
@@ -1190,16 +1234,20 @@ int xmc_test_gemm(int32_t device, int32_t layout, int32_t dtype, int32_t M, int3
   p.test_wait_limit = inject ? 2000000ll : 0;      // ~1 ms
   p.test_skip_tile = inject ? 0 : -1;
   layout &= 1;
-  p.m_rows = 128;
+  p.m_rows = pair ? 256 : 128;
   p.n_mtiles = cdiv(M, p.m_rows);
   p.status = status;
   int rc = XMC_OK;
   if (layout == 0) {
     if ((rc = make_map_kmajor(&ma, f8, A, K, M, K, 128))) { cudaFree(status); return rc; }
-    if ((rc = make_map_kmajor(&mb, f8, B, K, N, K, 256))) { cudaFree(status); return rc; }
+    // a CTA of a pair stages only its half of the B rows
+    if ((rc = make_map_kmajor(&mb, f8, B, K, N, K, pair ? 128 : 256))) { cudaFree(status); return rc; }
     p.k_steps = cdiv((long long)K * (f8 ? 1 : 2), 128);
-    rc = f8 ? launch_gemm<xmc::PlainPolicy<true, false>>(ma, mb, p, p.n_mtiles * p.n_ntiles, sm_count, st)
-            : launch_gemm<xmc::PlainPolicy<false, false>>(ma, mb, p, p.n_mtiles * p.n_ntiles, sm_count, st);
+    const int tiles = p.n_mtiles * p.n_ntiles;
+    if (pair) rc = f8 ? launch_gemm<xmc::PlainPolicy<true, false>, true>(ma, mb, p, tiles, sm_count, st)
+                      : launch_gemm<xmc::PlainPolicy<false, false>, true>(ma, mb, p, tiles, sm_count, st);
+    else rc = f8 ? launch_gemm<xmc::PlainPolicy<true, false>>(ma, mb, p, tiles, sm_count, st)
+                 : launch_gemm<xmc::PlainPolicy<false, false>>(ma, mb, p, tiles, sm_count, st);
   } else {
     if ((rc = make_map_mnmajor(&ma, A, M, K, M))) { cudaFree(status); return rc; }
     if ((rc = make_map_mnmajor(&mb, B, N, K, N))) { cudaFree(status); return rc; }

@@ -11,6 +11,23 @@ namespace xmc {
 
 __device__ __forceinline__ int round_up16(int v) { return (v + 15) & ~15; }
 
+// x / d for 0 <= x < 2^32 / d by one multiply: the roles recompute their tile coordinates once per tile,
+// and a real division (its reciprocal comes from the special-function pipe the forward epilogue
+// saturates) put hundreds of cycles between two tiles.  mul = floor(2^32 / d) + 1, or 0 for d == 1.
+struct FastDiv {
+  uint32_t mul;
+  int d;
+};
+__host__ __device__ inline FastDiv make_fastdiv(int d) {
+  FastDiv f;
+  f.d = d;
+  f.mul = d <= 1 ? 0u : (uint32_t)(0x100000000ull / (unsigned long long)d) + 1u;
+  return f;
+}
+__device__ __forceinline__ int fast_div(int x, const FastDiv& f) {
+  return f.mul == 0u ? x : (int)__umulhi((uint32_t)x, f.mul);
+}
+
 struct NoState {};
 
 // -------------------------------------------------------------------------------------------------
@@ -22,7 +39,8 @@ struct NoState {};
 struct FwdParams {
   int m_rows;              // label rows per M tile (128)
   int rows_valid;          // label rows of this scheduling chunk
-  int n_ltiles, n_btiles;  // label tiles (128) x batch tiles (256)
+  int n_ltiles, n_btiles;  // label tiles (m_rows) x batch tiles (256)
+  FastDiv div_btiles;      // make_fastdiv(n_btiles)
   int batch, bpad;         // valid batch rows, padded row length of G (multiple of 16)
   int k_steps;             // cdiv(d * elem_size, 128)
   float w_scale;
@@ -47,8 +65,11 @@ struct FwdPolicy {
   static constexpr bool kFp8 = FP8;
   static constexpr uint32_t kFmt = FP8 ? 0u : 1u;            // e4m3 | bf16
   static constexpr int kElemsPerRow = FP8 ? 128 : 64;
-  static constexpr int kEpiWarps = 8;
+  // sixteen epilogue warps (the converter variant keeps eight: its four converter warps already fill the
+  // register file)
+  static constexpr int kEpiWarps = CONV ? 8 : 16;
   static constexpr int kStages = CONV ? 3 : 4;
+  static constexpr int kStagesPair = 6;
   static constexpr bool kCTile = false;
   static constexpr int kCBufs = 1;
   static constexpr int kConv = CONV ? 1 : 0;
@@ -58,11 +79,12 @@ struct FwdPolicy {
   struct EpilogueState {
     float loss;
     int has_pos;
+    int next_bkt, next_beg, next_end;   // bucket range of the CTA's next tile, read a tile ahead
   };
 
   __device__ static int num_tiles(const Params& p) { return p.n_ltiles * p.n_btiles; }
   __device__ static void job(const Params& p, int tile, Job& j) {
-    j.t0 = tile / p.n_btiles;          // label tile
+    j.t0 = fast_div(tile, p.div_btiles);   // label tile
     j.t1 = tile - j.t0 * p.n_btiles;   // batch tile
     j.a0 = j.t0 * p.m_rows;
     j.b0 = j.t1 * kTileN;
@@ -73,13 +95,33 @@ struct FwdPolicy {
   __device__ static void epilogue_begin(const Params&, EpilogueState& st) {
     st.loss = 0.f;
     st.has_pos = 0;
+    st.next_bkt = -1;
+    st.next_beg = st.next_end = 0;
+  }
+  // The bucket offsets are two dependent-free global reads whose latency would otherwise sit between two
+  // epilogues (the epilogue warps are the busiest role of this kernel): issue them one tile ahead.
+  __device__ static void epilogue_prefetch(const Params& p, const Job& jn, EpilogueState& st) {
+    st.next_bkt = -1;
+    if (jn.a0 >= p.rows_valid) return;
+    st.next_bkt = p.tile_base + (jn.a0 >> 7);
+    st.next_beg = p.bucket_off[st.next_bkt];
+    st.next_end = p.bucket_off[st.next_bkt + 1];
   }
   // Build this warp's 32 rows of the positives bitmap (duplicates collapse: set semantics).
   // Each warp owns the bitmap words of its rows (quarter q) and of its column groups (phase h).
   __device__ static void epilogue_pre(const Params& p, const Job& j, SharedTail& sh, const EpiCtx& ec,
                                       EpilogueState& st) {
+    st.has_pos = 0;
+    if (j.a0 >= p.rows_valid) return;               // second CTA of a pair on an odd last tile: nothing to do
     const int bkt = p.tile_base + (j.a0 >> 7);      // buckets are per 128 label rows
-    const int beg = p.bucket_off[bkt], end = p.bucket_off[bkt + 1];
+    int beg, end;
+    if (bkt == st.next_bkt) {
+      beg = st.next_beg;
+      end = st.next_end;
+    } else {
+      beg = p.bucket_off[bkt];
+      end = p.bucket_off[bkt + 1];
+    }
     st.has_pos = end > beg;
     if (!st.has_pos) return;
     constexpr int kWordsPerRow = kTileN / 32;
@@ -98,6 +140,7 @@ struct FwdPolicy {
   }
   __device__ static void epilogue(const Params& p, const Job& j, uint32_t taddr, bool have_acc,
                                   SharedTail& sh, const EpiCtx& ec, EpilogueState& st) {
+    if (j.a0 >= p.rows_valid) return;               // whole CTA tile beyond the chunk (pairs only): G has no such rows
     const int row = ec.q * 32 + ec.lane;
     const int crow = j.a0 + row;
     const bool row_valid = crow < p.rows_valid;
@@ -198,8 +241,10 @@ struct FwdPolicy {
 // weights chunked.py:119 + stochastic_rounding_kernel.py:65-99).
 // -------------------------------------------------------------------------------------------------
 struct UpdParams {
+  int m_rows;              // label rows per M tile: 128, or 256 on CTA pairs
   int rows_valid;
   int n_ltiles, n_dtiles;
+  FastDiv div_dtiles;      // make_fastdiv(n_dtiles)
   int d;
   int k_steps;             // cdiv(bpad, 64)
   void* W;                 // first row of this scheduling chunk, row-major [rows x d]
@@ -238,16 +283,19 @@ struct UpdPolicy {
   __device__ static long long wait_limit(const Params&) { return kWaitLimitCycles; }
   __device__ static bool skip_load(const Params&, int, int) { return false; }
   static constexpr int kStages = W8 ? 3 : 4;
+  static constexpr int kStagesPair = W8 ? 5 : 6;
+  // the weight block: columns [c_col, c_col + 256) of the CTA's 128 rows; not stored back when the CTA's
+  // rows lie wholly beyond the chunk (second CTA of a pair on an odd last tile)
   __device__ static int c_col(const Job& j) { return j.b0; }
-  __device__ static int c_row(const Job& j) { return j.a0; }
+  __device__ static bool c_store(const Params& p, const Job& j) { return j.a0 < p.rows_valid; }
   static constexpr int kGroups = ((kTileN / 32) + (kEpiWarps / 4) - 1) / (kEpiWarps / 4);   // 32-column groups per thread and tile
   using EpilogueState = NoState;
 
   __device__ static int num_tiles(const Params& p) { return p.n_ltiles * p.n_dtiles; }
   __device__ static void job(const Params& p, int tile, Job& j) {
-    j.t0 = tile / p.n_dtiles;
+    j.t0 = fast_div(tile, p.div_dtiles);
     j.t1 = tile - j.t0 * p.n_dtiles;
-    j.a0 = j.t0 * kTileM;     // rows of G
+    j.a0 = j.t0 * p.m_rows;   // rows of G
     j.b0 = j.t1 * kTileN;     // rows of X^T = feature index
     j.k_begin = 0;
     j.k_steps = p.k_steps;
@@ -257,6 +305,7 @@ struct UpdPolicy {
   __device__ static void epilogue_end(const Params&, SharedTail&, const EpiCtx&, EpilogueState&) {}
 
   __device__ static void epilogue_pre(const Params&, const Job&, SharedTail&, const EpiCtx&, EpilogueState&) {}
+  __device__ static void epilogue_prefetch(const Params&, const Job&, EpilogueState&) {}
   __device__ static void load_acc(uint32_t taddr, bool have_acc, uint32_t (&v)[32]) {
     if (have_acc) {
       tmem_ld32(taddr, v);
@@ -404,45 +453,59 @@ struct UpdPolicy {
     return make_uint2(ow[0], ow[1]);
   }
 
-  // the whole tile for e4m3 weights: 4 * kGroups sub-blocks of 8 columns per thread
+  // the whole tile for e4m3 weights: 2 * kGroups sub-blocks of 16 columns per thread.  The two halves of
+  // a sub-block (8 columns, one Philox call each) are independent chains in one basic block: a warp has
+  // two of the long multiply-xor chains to interleave, which is what lets four warps per scheduler fill
+  // its issue slots.
   __device__ static void epilogue_w8(const Params& p, const Job& j, uint32_t taddr, bool have_acc, const EpiCtx& ec) {
     const int row = ec.q * 32 + ec.lane;
     const int crow = j.a0 + row;
     const bool row_valid = crow < p.rows_valid;
     const unsigned long long erow = p.elem0 + (unsigned long long)crow * p.d + j.b0;
 #pragma unroll 1
-    for (int sb = 0; sb < 4 * kGroups; ++sb) {
-      const int c0 = 32 * (ec.h + ec.nsplit * (sb >> 2)) + 8 * (sb & 3);
+    for (int sb = 0; sb < 2 * kGroups; ++sb) {
+      const int c0 = 32 * (ec.h + ec.nsplit * (sb >> 1)) + 16 * (sb & 1);
       if (c0 >= j.n_eff) break;                          // warp-uniform
       // tcgen05.ld / wait::ld are warp-wide (.sync.aligned): issued by all 32 lanes, outside every
-      // lane-dependent branch; the load is asynchronous, so the random bits are drawn while it flies
-      uint32_t v[8];
+      // lane-dependent branch; the loads are asynchronous, so the random bits are drawn while they fly
+      uint32_t va[8], vb[8];
       if (have_acc) {
-        tmem_ld8(taddr + c0, v);
+        tmem_ld8(taddr + c0, va);
+        tmem_ld8(taddr + c0 + 8, vb);
       } else {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = 0u;
+        for (int i = 0; i < 8; ++i) va[i] = vb[i] = 0u;
       }
-      uint2* wslot = ctile_ptr8(ec.ctile, row, c0);
-      const uint2 wraw = *wslot;                         // rows / columns outside the tensor were zero-filled
-      uint4 r = make_uint4(0u, 0u, 0u, 0u);
-      if (SR) r = random8(p, erow + c0);
-      if (have_acc) tmem_ld_wait_for(v);
-      uint2 out;
-      bool bad = false;
+      // 16 weight bytes: one 16-byte piece of the swizzled block
+      uint4* wslot = reinterpret_cast<uint4*>(ctile_ptr8(ec.ctile, row, c0));
+      const uint4 wraw = *wslot;                         // rows / columns outside the tensor were zero-filled
+      uint4 ra = make_uint4(0u, 0u, 0u, 0u), rb = ra;
+      if (SR) {
+        ra = random8(p, erow + c0);
+        rb = random8(p, erow + c0 + 8);
+      }
+      if (have_acc) tmem_ld_wait_for(va, vb);
+      const uint2 wa = make_uint2(wraw.x, wraw.y), wb = make_uint2(wraw.z, wraw.w);
+      uint2 oa, ob;
       bool kahan_row = false;
       if constexpr (KAHAN) kahan_row = crow < p.kahan_rows;
       if (kahan_row) {
-        out = wraw;
-        if (row_valid && j.b0 + c0 < p.d) {
+        oa = wa;
+        ob = wb;
+        if (row_valid) {
           uint8_t* krow = reinterpret_cast<uint8_t*>(p.kahan) + ((size_t)crow * p.d + j.b0 + c0) * (p.kahan_e5m2 ? 1 : 2);
-          out = update8_kahan(p, v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7], wraw, r, krow);
+          if (j.b0 + c0 < p.d) oa = update8_kahan(p, va[0], va[1], va[2], va[3], va[4], va[5], va[6], va[7], wa, ra, krow);
+          if (j.b0 + c0 + 8 < p.d)
+            ob = update8_kahan(p, vb[0], vb[1], vb[2], vb[3], vb[4], vb[5], vb[6], vb[7], wb, rb, krow + (p.kahan_e5m2 ? 8 : 16));
         }
       } else {
-        out = update8(p, v, wraw, r, bad);
-        if (bad) out = update8_careful(p, v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7], wraw, r);
+        bool bad_a = false, bad_b = false;
+        oa = update8(p, va, wa, ra, bad_a);
+        ob = update8(p, vb, wb, rb, bad_b);
+        if (bad_a) oa = update8_careful(p, va[0], va[1], va[2], va[3], va[4], va[5], va[6], va[7], wa, ra);
+        if (bad_b) ob = update8_careful(p, vb[0], vb[1], vb[2], vb[3], vb[4], vb[5], vb[6], vb[7], wb, rb);
       }
-      if (row_valid) *wslot = out;                       // in place; the engine stores the block back with TMA
+      if (row_valid) *wslot = make_uint4(oa.x, oa.y, ob.x, ob.y);   // in place; the engine stores the block back with TMA
     }
   }
 
@@ -482,6 +545,7 @@ struct UpdPolicy {
 
   __device__ static void epilogue(const Params& p, const Job& j, uint32_t taddr, bool have_acc,
                                   SharedTail&, const EpiCtx& ec, EpilogueState& st) {
+    if (j.a0 >= p.rows_valid) return;               // whole CTA tile beyond the chunk (pairs only)
     if constexpr (W8) {
       epilogue_w8(p, j, taddr, have_acc, ec);
     } else {
@@ -549,6 +613,7 @@ struct LogitsPolicy {
   }
   __device__ static void epilogue_begin(const Params&, EpilogueState&) {}
   __device__ static void epilogue_pre(const Params&, const Job&, SharedTail&, const EpiCtx&, EpilogueState&) {}
+  __device__ static void epilogue_prefetch(const Params&, const Job&, EpilogueState&) {}
   __device__ static void epilogue_end(const Params&, SharedTail&, const EpiCtx&, EpilogueState&) {}
   __device__ static void epilogue(const Params& p, const Job& j, uint32_t taddr, bool have_acc,
                                   SharedTail&, const EpiCtx& ec, EpilogueState&) {
@@ -664,6 +729,7 @@ struct TopkPolicy {
     j.n_eff = min(kTileN, round_up16(p.rows - j.b0));
   }
   __device__ static void epilogue_begin(const Params&, EpilogueState& st) { st.list = -1; }
+  __device__ static void epilogue_prefetch(const Params&, const Job&, EpilogueState&) {}
   __device__ static void epilogue_pre(const Params& p, const Job& j, SharedTail&, const EpiCtx& ec, EpilogueState& st) {
     const int b = j.a0 + ec.q * 32 + ec.lane;
     if (st.list < 0) {
@@ -878,6 +944,7 @@ struct PlainPolicy {
   static constexpr int kElemsPerRow = FP8 ? 128 : 64;
   static constexpr int kEpiWarps = 8;
   static constexpr int kStages = 4;
+  static constexpr int kStagesPair = 6;
   static constexpr bool kCTile = false;
   static constexpr int kCBufs = 1;
   static constexpr int kConv = 0;
@@ -898,6 +965,7 @@ struct PlainPolicy {
   }
   __device__ static void epilogue_begin(const Params&, EpilogueState&) {}
   __device__ static void epilogue_pre(const Params&, const Job&, SharedTail&, const EpiCtx&, EpilogueState&) {}
+  __device__ static void epilogue_prefetch(const Params&, const Job&, EpilogueState&) {}
   __device__ static void epilogue_end(const Params&, SharedTail&, const EpiCtx&, EpilogueState&) {}
   __device__ static void epilogue(const Params& p, const Job& j, uint32_t taddr, bool have_acc,
                                   SharedTail&, const EpiCtx& ec, EpilogueState&) {

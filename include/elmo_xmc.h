@@ -223,6 +223,7 @@ int xmc_noalloc_check(int32_t device, void* stream);
  *   layout 0: A [M x K], B [N x K] both K-major (row-major as written), dtype XMC_DT_BF16 or XMC_DT_E4M3
  *   layout 1: A given as [K x M], B as [K x N] row-major (both "MN-major"), dtype XMC_DT_BF16
  *   layout | 2: same contraction, but D is not stored (times the main loop alone)
+ *   layout | 4 (with layout 0): the same contraction on CTA pairs (clusters of two, 256-row tiles)
  *   layout | 8 (with layout 0): exercises the kernels' failure handling without faulting anything: the
  *               producer leaves out one operand load of tile 0 and every wait of the launch is limited to
  *               about a millisecond, so the wait for that load gives up, the CTA unwinds, and the call
