@@ -472,7 +472,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
-        if constexpr (PAIR) mbar_arrive_cluster_relaxed(tmem_empty_leader + 8u * buf);
+        if constexpr (PAIR) mbar_arrive_remote(tmem_empty_leader + 8u * buf);
         else mbar_arrive(tmem_empty_leader + 8u * buf);
       }
       if constexpr (Policy::kCTile) {

@@ -300,11 +300,13 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n"
                "barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// Arrival on a barrier of the peer CTA that publishes no memory: the accumulator hand-back (the TMEM
-// loads it follows have completed in program order, tcgen05.fence::before_thread_sync precedes it).
-// A release at cluster scope would make the thread wait for all its earlier global stores first.
-__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+// Arrival on a barrier that may live in the peer CTA of the pair (cluster address), with the default
+// semantics of mbarrier.arrive: release at CTA scope.  What the arrival hands over is either no memory at
+// all (an accumulator that has been read) or shared memory of this CTA that a proxy fence has already made
+// visible to the tensor cores.  A release at cluster scope here costs well over a thousand cycles per
+// arrival (measured: it more than doubled the grad_X main loop).
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // TMA load into this CTA's shared memory whose completion bytes are counted on a barrier that may
 // live in the peer CTA of the pair (cluster address).  Not a multicast: one destination.
@@ -314,6 +316,14 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtens
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
       "[%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_dst), "l"((uint64_t)map), "r"(bar_cluster), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar_cluster,
+                                                 int32_t c0, int32_t c1, int32_t c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_dst), "l"((uint64_t)map), "r"(bar_cluster), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_result, uint32_t ncols) {

@@ -112,10 +112,10 @@ int make_map(CUtensorMap* m, bool e4m3, const void* base, uint64_t inner, uint64
   return XMC_OK;
 }
 // [rows x cols] row-major matrix seen as [cols/64 blocks][rows][64 elements]: one box fetches
-// `box_rows` rows of 4 consecutive 64-element blocks, laid out block after block in shared memory
+// `box_rows` rows of `box_blocks` consecutive 64-element blocks, laid out block after block in shared memory
 // (each block = box_rows rows of 64 elements).  Blocks/rows outside the matrix read as zero.
 int make_map_blocked(CUtensorMap* m, bool e4m3, const void* base, uint64_t cols, uint64_t rows,
-                     uint64_t row_stride_elems, uint32_t box_rows, bool swizzle) {
+                     uint64_t row_stride_elems, uint32_t box_rows, bool swizzle, uint32_t box_blocks = 4) {
   EncodeFn enc;
   if (int rc = get_encode(&enc)) return rc;
   const uint32_t es = e4m3 ? 1 : 2;
@@ -125,7 +125,7 @@ int make_map_blocked(CUtensorMap* m, bool e4m3, const void* base, uint64_t cols,
   MapKey key;
   memset(&key, 0, sizeof(key));
   key.base = (uint64_t)(uintptr_t)base; key.a = cols; key.b = rows; key.c = row_stride_elems;
-  key.kind = 3; key.e4m3 = e4m3; key.box0 = 64; key.box1 = box_rows; key.swizzle = swizzle;
+  key.kind = 3; key.e4m3 = e4m3; key.box0 = 64; key.box1 = box_rows; key.swizzle = swizzle; key.pad = box_blocks;
   MapSlot* slot = map_slot(key);
   if (slot->used && slot->key == key) {
     *m = slot->map;
@@ -133,7 +133,7 @@ int make_map_blocked(CUtensorMap* m, bool e4m3, const void* base, uint64_t cols,
   }
   const cuuint64_t dims[3] = {64, rows, cols / 64};
   const cuuint64_t strides[2] = {row_stride_elems * es, 64ull * es};
-  const cuuint32_t box[3] = {64, box_rows, 4};
+  const cuuint32_t box[3] = {64, box_rows, box_blocks};
   const cuuint32_t estr[3] = {1, 1, 1};
   const CUresult r = enc(m, e4m3 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
                          const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -200,16 +200,26 @@ cudaError_t launch_pdl(Kern kern, int grid, int block, size_t smem, cudaStream_t
   return cudaLaunchKernelEx(&cfg, kern, args...);
 }
 
-// dynamic shared memory opt-in of the grad_X kernels, once per device
-int gradx_configure() {
+// dynamic shared memory opt-in of the grad_X kernels, once per device; *max_pairs = CTA pairs of the pair
+// kernel the device holds at once
+int gradx_configure(int sm_count, int* max_pairs) {
   static std::atomic<uint64_t> configured{0};
+  static std::atomic<int> pairs[64];
   int dev = 0;
   CU_TRY(cudaGetDevice(&dev));
-  if (!((configured.load(std::memory_order_relaxed) >> (dev & 63)) & 1ull)) {
-    CU_TRY(cudaFuncSetAttribute(xmc::gradx_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, xmc::kGxSmemBytes));
-    CU_TRY(cudaFuncSetAttribute(xmc::gradx_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, xmc::kGxSmemBytes));
-    configured.fetch_or(1ull << (dev & 63));
+  if (!((configured.load(std::memory_order_acquire) >> (dev & 63)) & 1ull)) {
+    CU_TRY(cudaFuncSetAttribute(xmc::gradx_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, xmc::kGxSmemBytes<false>));
+    CU_TRY(cudaFuncSetAttribute(xmc::gradx_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, xmc::kGxSmemBytes<false>));
+    CU_TRY(cudaFuncSetAttribute(xmc::gradx_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, xmc::kGxSmemBytes<true>));
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute at[2];
+    launch_config(&cfg, at, sm_count / 2 * 2, xmc::kGxThreads, xmc::kGxSmemBytes<true>, nullptr, 2);
+    int n = 0;
+    CU_TRY(cudaOccupancyMaxActiveClusters(&n, xmc::gradx_kernel<true, true>, &cfg));
+    pairs[dev & 63].store(std::max(0, std::min(n, sm_count / 2)), std::memory_order_relaxed);
+    configured.fetch_or(1ull << (dev & 63), std::memory_order_release);
   }
+  *max_pairs = pairs[dev & 63].load(std::memory_order_relaxed);
   return XMC_OK;
 }
 
@@ -668,8 +678,15 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
   }
 
   // --- grad_X partial geometry ---
-  const int n_bt = cdiv(bpad, 256), n_dt = cdiv(d, 256);
-  int n_splits = std::max(1, h->sm_count / (n_bt * n_dt));
+  // On CTA pairs (512-row batch tiles) when the weights are e4m3, every feature tile is whole and both
+  // CTAs of a pair have batch rows to work on; otherwise one CTA per 256 x 256 tile.
+  static const bool no_pairs_gx = getenv("XMC_NO_PAIRS") != nullptr;
+  int gx_max_pairs = 0;
+  if (int rc = gradx_configure(h->sm_count, &gx_max_pairs)) return rc;
+  const int n_dt = cdiv(d, 256);
+  const bool pair_gx = !no_pairs_gx && w8 && d % 256 == 0 && bpad >= 256 && gx_max_pairs >= cdiv(bpad, 512) * n_dt;
+  const int n_bt = cdiv(bpad, pair_gx ? 512 : 256);
+  int n_splits = std::max(1, (pair_gx ? gx_max_pairs : h->sm_count) / (n_bt * n_dt));
   while (n_splits > 1 && (int64_t)n_splits * bpad * d > h->partial_floats) --n_splits;
   if ((int64_t)n_splits * bpad * d > h->partial_floats) return fail(XMC_ERR_STATE, "grad_X workspace too small");
 
@@ -707,7 +724,7 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
     if (int rc = make_map_kmajor(&map_xt, false, h->xt, bpad, std::max(d, 256), bpad, pair_upd ? 128 : 256)) return rc;
     if (int rc = make_map_kmajor(&map_g_k, false, h->G, bpad, h->g_rows, bpad, 128)) return rc;
   }
-  if (int rc = make_map_blocked(&map_g_mn, false, h->G, bpad, h->g_rows, bpad, xmc::kGxRows, true)) return rc;
+  if (int rc = make_map_blocked(&map_g_mn, false, h->G, bpad, h->g_rows, bpad, xmc::kGxRows, true, pair_gx ? 2 : 4)) return rc;
 
   const float lr_eff = lr / h->cfg.w_scale;
   const int tiles_per_sched = h->sched / 128;
@@ -774,7 +791,7 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
       CUtensorMap map_w_gx;
       if (w8) {
         // raw e4m3 rows, unswizzled boxes of 32 rows x 256 features; converted inside the kernel
-        if (int rc2 = make_map_blocked(&map_w_gx, true, wbase, d, rows_valid, d, xmc::kGxRows, false)) return rc2;
+        if (int rc2 = make_map_blocked(&map_w_gx, true, wbase, d, rows_valid, d, xmc::kGxRows, false, pair_gx ? 2 : 4)) return rc2;
       } else {
         if (int rc2 = make_map_blocked(&map_w_gx, false, wbase, d, rows_valid, d, xmc::kGxRows, true)) return rc2;
       }
@@ -791,12 +808,15 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
       mark(h, K_GRADX, st);
       {
         const int grid = n_bt * n_dt * n_splits;
-        if (w8) {
-          if (int rc2 = gradx_configure()) return rc2;
-          CU_TRY(launch_pdl(xmc::gradx_kernel<true>, grid, xmc::kGxThreads, xmc::kGxSmemBytes, st, map_g_mn, map_w_gx, gp));
+        if (pair_gx) {
+          cudaLaunchConfig_t cfg;
+          cudaLaunchAttribute at[2];
+          launch_config(&cfg, at, 2 * grid, xmc::kGxThreads, xmc::kGxSmemBytes<true>, st, 2);
+          CU_TRY(cudaLaunchKernelEx(&cfg, xmc::gradx_kernel<true, true>, map_g_mn, map_w_gx, gp));
+        } else if (w8) {
+          CU_TRY(launch_pdl(xmc::gradx_kernel<true, false>, grid, xmc::kGxThreads, xmc::kGxSmemBytes<false>, st, map_g_mn, map_w_gx, gp));
         } else {
-          if (int rc2 = gradx_configure()) return rc2;
-          CU_TRY(launch_pdl(xmc::gradx_kernel<false>, grid, xmc::kGxThreads, xmc::kGxSmemBytes, st, map_g_mn, map_w_gx, gp));
+          CU_TRY(launch_pdl(xmc::gradx_kernel<false, false>, grid, xmc::kGxThreads, xmc::kGxSmemBytes<false>, st, map_g_mn, map_w_gx, gp));
         }
         CU_TRY(cudaGetLastError());
       }
@@ -1138,8 +1158,8 @@ int xmc_large_k_matmul_noalloc(int32_t device, const void* a_bf16, const void* b
     if (cc_major != 10) return fail(XMC_ERR_CUDA, "device %d is not sm_100", device);
     float* ptr = nullptr;
     CU_TRY(cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch));
-    CU_TRY(cudaFuncSetAttribute(xmc::gradx_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, xmc::kGxSmemBytes));
-    CU_TRY(cudaFuncSetAttribute(xmc::gradx_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, xmc::kGxSmemBytes));
+    CU_TRY(cudaFuncSetAttribute(xmc::gradx_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, xmc::kGxSmemBytes<false>));
+    CU_TRY(cudaFuncSetAttribute(xmc::gradx_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, xmc::kGxSmemBytes<false>));
     // two threads racing through the set-up compute the same address; the publication itself is atomic
     g_noalloc_ptr[device].store(ptr, std::memory_order_release);
   }
@@ -1167,8 +1187,8 @@ int xmc_large_k_matmul_noalloc(int32_t device, const void* a_bf16, const void* b
   gp.partial = scratch;
   gp.status = status;           // zero in the library image; set by a kernel that gave up a wait, read and
                                 // cleared by xmc_noalloc_check
-  if (f8) xmc::gradx_kernel<true><<<tiles * n_splits, xmc::kGxThreads, xmc::kGxSmemBytes, st>>>(map_a, map_b, gp);
-  else xmc::gradx_kernel<false><<<tiles * n_splits, xmc::kGxThreads, xmc::kGxSmemBytes, st>>>(map_a, map_b, gp);
+  if (f8) xmc::gradx_kernel<true, false><<<tiles * n_splits, xmc::kGxThreads, xmc::kGxSmemBytes<false>, st>>>(map_a, map_b, gp);
+  else xmc::gradx_kernel<false, false><<<tiles * n_splits, xmc::kGxThreads, xmc::kGxSmemBytes<false>, st>>>(map_a, map_b, gp);
   CU_TRY(cudaGetLastError());
   const long long total = (long long)m * n;
   const int blocks = (int)std::min<long long>((total + 255) / 256, (long long)sm_count * 8);
