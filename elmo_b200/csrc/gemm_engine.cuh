@@ -176,7 +176,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   tc_fence_before();
   if constexpr (PAIR) cluster_sync_all();   // both CTAs' barriers exist before anything remote happens
   else __syncthreads();
-  pdl_wait();                               // nothing above touches global memory written by earlier kernels
+  // Nothing above touches global memory written by earlier kernels.  A policy whose operands no earlier
+  // kernel of the stream's recent past writes (kEarlyLoads) lets the producer and MMA warps go ahead: the
+  // first tiles' operands then stream in while the previous kernel drains; its epilogue warps, which read
+  // and write what other kernels share, wait as everybody else does.
+  if (!(Policy::kEarlyLoads && warp <= 1)) pdl_wait();
   tc_fence_after();
   const uint32_t tmem_base = sh.tmem_base;
 
@@ -411,7 +415,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         const int c_col = Policy::c_col(job);
         if constexpr (PAIR) job.a0 += kTileM * (int)rank;
         const uint32_t cb = t_local % kCBufs, cph = (t_local / kCBufs) & 1u;
-        if (!__all_sync(0xffffffffu, mbar_wait_relaxed(smem_u32(&sh.c_done[cb]), cph, &sh.ctl, p.status, 620 + (int)cb))) break;
+        if (!mbar_wait_warp(smem_u32(&sh.c_done[cb]), cph, &sh.ctl, p.status, 620 + (int)cb)) break;
         if (lane == 0) {
           const uint32_t src = smem_u32(smem_c + cb * kCTileBytes);
           if (Policy::c_store(p, job)) {
@@ -457,7 +461,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         if constexpr (PAIR) next.a0 += kTileM * (int)rank;
         Policy::epilogue_prefetch(p, next, st);
       }
-      if (!mbar_wait_relaxed(smem_u32(&sh.tmem_full[buf]), aph, &sh.ctl, p.status, 400 + (int)buf)) break;
+      if (!mbar_wait(smem_u32(&sh.tmem_full[buf]), aph, &sh.ctl, p.status, 400 + (int)buf)) break;
       const uint32_t cb = t_local % kCBufs, cph = (t_local / kCBufs) & 1u;
       if constexpr (Policy::kCTile) {
         if (!mbar_wait(smem_u32(&sh.c_full[cb]), cph, &sh.ctl, p.status, 610 + (int)cb)) break;

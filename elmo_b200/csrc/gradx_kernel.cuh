@@ -267,7 +267,7 @@ gradx_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant__ 
         if (++rs == (uint32_t)kRawStages) { rs = 0; rph ^= 1u; }
       }
     }
-    if (ok && mbar_wait_relaxed(smem_u32(&sh.tmem_full), 0u, &sh.ctl, p.status, 560)) {
+    if (ok && mbar_wait(smem_u32(&sh.tmem_full), 0u, &sh.ctl, p.status, 560)) {
       tc_fence_after();
       const int q = warp & 3;
       const int hm = cw >> 2;                                     // warps 2..5 -> accumulator 0, 6..9 -> 1
