@@ -83,6 +83,8 @@ struct SharedTail {
   Ctl ctl;
 };
 constexpr int kBitmapBytes = kTileM * (kTileN / 32) * 4;
+// roles of a CTA, as bits of Policy::kWaitRoles (who waits for the previous kernels of the stream)
+constexpr int kRoleProducer = 1, kRoleMma = 2, kRoleEpilogue = 4, kRoleExtra = 8, kRoleAll = 15;
 constexpr int kConvWarps = 4;
 template <class Policy>
 __host__ __device__ constexpr int conv_rows() { return Policy::kConv == 1 ? kTileM : (Policy::kConv == 2 ? kTileN : 0); }
@@ -176,11 +178,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   tc_fence_before();
   if constexpr (PAIR) cluster_sync_all();   // both CTAs' barriers exist before anything remote happens
   else __syncthreads();
-  // Nothing above touches global memory written by earlier kernels.  A policy whose operands no earlier
-  // kernel of the stream's recent past writes (kEarlyLoads) lets the producer and MMA warps go ahead: the
-  // first tiles' operands then stream in while the previous kernel drains; its epilogue warps, which read
-  // and write what other kernels share, wait as everybody else does.
-  if (!(Policy::kEarlyLoads && warp <= 1)) pdl_wait();
+  // Nothing above touches global memory written by earlier kernels.  From here on a role waits for the
+  // kernels before this one only if it has to (Policy::kWaitRoles): a producer whose operands no recent
+  // kernel writes streams the first tiles in while the previous kernel drains, and the MMA issuer, which
+  // touches shared and tensor memory only, goes with it; whoever reads or writes what the previous
+  // kernels share waits.
+  {
+    const int role = warp == 0 ? kRoleProducer : warp == 1 ? kRoleMma : warp < 2 + Policy::kEpiWarps ? kRoleEpilogue : kRoleExtra;
+    if (Policy::kWaitRoles & role) pdl_wait();
+  }
   tc_fence_after();
   const uint32_t tmem_base = sh.tmem_base;
 

@@ -127,7 +127,22 @@ gradx_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant__ 
   tc_fence_before();
   if constexpr (PAIR) cluster_sync_all();   // both CTAs' barriers exist before anything remote happens
   else __syncthreads();
-  pdl_wait();                               // nothing above touches global memory written by earlier kernels
+  // The raw weight tiles depend on nothing before this kernel (the weights were last written a step ago):
+  // the producer sends for its first ring of them, then everybody waits for the kernel that writes G.
+  if constexpr (CONVERT) {
+    if (warp == 0) {
+      const int krow0 = k_begin * kGxRows;
+      for (int r = 0; r < kRawStages && r < k_steps; ++r) {
+        if (elect_one()) {
+          const uint32_t rb = smem_u32(&sh.raw_full[r]);
+          mbar_arrive_expect_tx(rb, kRawBytes);
+          tma_load_3d(smem_u32(smem_r + r * kRawBytes), &map_w, rb, 0, krow0 + r * kGxRows, c_cta >> 6);
+        }
+        __syncwarp();
+      }
+    }
+  }
+  pdl_wait();
   tc_fence_after();
   const uint32_t tmem_base = sh.tmem_base;
   // barriers the two CTAs of a pair share live in the leader
@@ -144,17 +159,26 @@ gradx_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant__ 
     {
       uint32_t s = 0, ph = 0, rs = 0, rph = 0;
       int krow = k_begin * kGxRows;
+      // the first ring of raw weight tiles is already on its way (see above)
+      int raw_ahead = 0;
+      if constexpr (CONVERT) {
+        raw_ahead = min(kRawStages, k_steps);
+        rph = raw_ahead == kRawStages ? 1u : 0u;
+        rs = raw_ahead == kRawStages ? 0u : (uint32_t)raw_ahead;
+      }
       for (int i = 0; i < k_steps; ++i, krow += kGxRows) {
         if constexpr (CONVERT) {
-          if (!mbar_wait_warp(smem_u32(&sh.raw_empty[rs]), rph ^ 1u, &sh.ctl, p.status, 500 + (int)rs)) break;
-          if (elect_one()) {
-            const uint32_t rb = smem_u32(&sh.raw_full[rs]);
-            mbar_arrive_expect_tx(rb, kRawBytes);
-            // one box: [feature blocks][32 rows][64 B]
-            tma_load_3d(smem_u32(smem_r + rs * kRawBytes), &map_w, rb, 0, krow, c_cta >> 6);
+          if (i + raw_ahead < k_steps) {                          // the raw tile raw_ahead k-steps on
+            if (!mbar_wait_warp(smem_u32(&sh.raw_empty[rs]), rph ^ 1u, &sh.ctl, p.status, 500 + (int)rs)) break;
+            if (elect_one()) {
+              const uint32_t rb = smem_u32(&sh.raw_full[rs]);
+              mbar_arrive_expect_tx(rb, kRawBytes);
+              // one box: [feature blocks][32 rows][64 B]
+              tma_load_3d(smem_u32(smem_r + rs * kRawBytes), &map_w, rb, 0, krow + raw_ahead * kGxRows, c_cta >> 6);
+            }
+            __syncwarp();
+            if (++rs == (uint32_t)kRawStages) { rs = 0; rph ^= 1u; }
           }
-          __syncwarp();
-          if (++rs == (uint32_t)kRawStages) { rs = 0; rph ^= 1u; }
         }
         if (!mbar_wait_warp(smem_u32(&sh.mma_done[s]), ph ^ 1u, &sh.ctl, p.status, 510 + (int)s)) break;
         if (elect_one()) {

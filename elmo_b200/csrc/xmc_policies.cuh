@@ -75,8 +75,9 @@ struct FwdPolicy {
   static constexpr int kConv = CONV ? 1 : 0;
   static constexpr bool kBitmap = true;
   // W of this chunk was last written a step ago and the quantised X by a kernel that ordinary (fully
-  // serialising) launches separate from this one: the operand loads need not wait for the kernels before
-  static constexpr bool kEarlyLoads = true;
+  // serialising) launches separate from this one: the operand loads need not wait for the kernels before.
+  // The epilogue overwrites G, which the previous chunk's kernels read: it waits.
+  static constexpr int kWaitRoles = kRoleEpilogue | kRoleExtra;
   __device__ static long long wait_limit(const Params&) { return kWaitLimitCycles; }
   __device__ static bool skip_load(const Params&, int, int) { return false; }
   struct EpilogueState {
@@ -283,7 +284,7 @@ struct UpdPolicy {
   static constexpr int kCBufs = 2;
   static constexpr int kConv = 0;
   static constexpr bool kBitmap = false;
-  static constexpr bool kEarlyLoads = false;
+  static constexpr int kWaitRoles = kRoleAll;
   __device__ static long long wait_limit(const Params&) { return kWaitLimitCycles; }
   __device__ static bool skip_load(const Params&, int, int) { return false; }
   static constexpr int kStages = W8 ? 3 : 4;
@@ -602,7 +603,7 @@ struct LogitsPolicy {
   static constexpr int kCBufs = 1;
   static constexpr int kConv = CONV ? 2 : 0;      // the weights are the B operand here
   static constexpr bool kBitmap = false;
-  static constexpr bool kEarlyLoads = false;
+  static constexpr int kWaitRoles = kRoleAll;
   __device__ static long long wait_limit(const Params&) { return kWaitLimitCycles; }
   __device__ static bool skip_load(const Params&, int, int) { return false; }
   using EpilogueState = NoState;
@@ -714,7 +715,7 @@ struct TopkPolicy {
   static constexpr int kCBufs = 1;
   static constexpr int kConv = CONV ? 2 : 0;
   static constexpr bool kBitmap = false;
-  static constexpr bool kEarlyLoads = false;
+  static constexpr int kWaitRoles = kRoleAll;
   __device__ static long long wait_limit(const Params&) { return kWaitLimitCycles; }
   __device__ static bool skip_load(const Params&, int, int) { return false; }
   struct EpilogueState {
@@ -955,7 +956,7 @@ struct PlainPolicy {
   static constexpr int kCBufs = 1;
   static constexpr int kConv = 0;
   static constexpr bool kBitmap = false;
-  static constexpr bool kEarlyLoads = false;
+  static constexpr int kWaitRoles = kRoleAll;
   // failure-injection of the self-test: a shortened wait limit and one operand load left out
   __device__ static long long wait_limit(const Params& p) { return p.test_wait_limit > 0 ? p.test_wait_limit : kWaitLimitCycles; }
   __device__ static bool skip_load(const Params& p, int tile, int k) { return tile == p.test_skip_tile && k == 1; }
