@@ -684,7 +684,7 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
   int gx_max_pairs = 0;
   if (int rc = gradx_configure(h->sm_count, &gx_max_pairs)) return rc;
   const int n_dt = cdiv(d, 256);
-  const bool pair_gx = !no_pairs_gx && w8 && d % 256 == 0 && bpad >= 256 && gx_max_pairs >= cdiv(bpad, 512) * n_dt;
+  const bool pair_gx = !no_pairs_gx && w8 && d % 256 == 0 && bpad >= 256 && gx_max_pairs >= 1;
   const int n_bt = cdiv(bpad, pair_gx ? 512 : 256);
   int n_splits = std::max(1, (pair_gx ? gx_max_pairs : h->sm_count) / (n_bt * n_dt));
   while (n_splits > 1 && (int64_t)n_splits * bpad * d > h->partial_floats) --n_splits;

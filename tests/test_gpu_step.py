@@ -78,12 +78,14 @@ def test_fp8_step_matches_oracle(L, d, B, nc, sched, rounding):
     assert changed > 0                                                # the step did update weights
 
 
-@pytest.mark.parametrize("B", [1100, 2048])
-def test_fp8_step_large_batch(B):
+@pytest.mark.parametrize("B,d", [(1100, 128), (2048, 128), (1100, 512), (832, 256)])
+def test_fp8_step_large_batch(B, d):
     """Several batch tiles in every kernel (forward N-tiles, grad_X M-tiles incl. a half-filled last
-    one, update K-steps), as the label-sharded runs see with an all-gathered batch."""
+    one, update K-steps), as the label-sharded runs see with an all-gathered batch.  d = 128 takes the
+    single-CTA grad_X kernel, d = 256 / 512 the CTA-pair one with several 512-row batch tiles, the last
+    of them partly (832: its second accumulator covers 64 valid rows) or half empty."""
     from oracle import xmc_oracle as O
-    L, d = 1536, 128
+    L = 1536
     w, x, lab = _inputs(L, d, B, 4 * B, seed=B)
     want_w, want_gx, want_loss = O.fp8_chunked_step([w], x, lab, 0.1, rounding="sr", seed=5, step=2,
                                                     compute_loss=True)
