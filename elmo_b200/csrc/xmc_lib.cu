@@ -680,11 +680,12 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
   // --- grad_X partial geometry ---
   // On CTA pairs (512-row batch tiles) when the weights are e4m3, every feature tile is whole and both
   // CTAs of a pair have batch rows to work on; otherwise one CTA per 256 x 256 tile.
-  static const bool no_pairs_gx = getenv("XMC_NO_PAIRS") != nullptr;
+  static const bool no_pairs = getenv("XMC_NO_PAIRS") != nullptr;
   int gx_max_pairs = 0;
   if (int rc = gradx_configure(h->sm_count, &gx_max_pairs)) return rc;
+  const bool pairs_ok = !no_pairs && gx_max_pairs >= 1;   // a device that cannot hold a pair runs everything on single CTAs
   const int n_dt = cdiv(d, 256);
-  const bool pair_gx = !no_pairs_gx && w8 && d % 256 == 0 && bpad >= 256 && gx_max_pairs >= 1;
+  const bool pair_gx = pairs_ok && w8 && d % 256 == 0 && bpad >= 256;
   const int n_bt = cdiv(bpad, pair_gx ? 512 : 256);
   int n_splits = std::max(1, (pair_gx ? gx_max_pairs : h->sm_count) / (n_bt * n_dt));
   while (n_splits > 1 && (int64_t)n_splits * bpad * d > h->partial_floats) --n_splits;
@@ -709,9 +710,8 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
   const size_t xrows = (size_t)std::max(h->bpad_max, 256);
   // CTA pairs (256-row label tiles, each CTA staging half of the other operand's rows) for the kernels
   // that take their operands as stored: the FP8 and bf16 forward, every update
-  static const bool no_pairs = getenv("XMC_NO_PAIRS") != nullptr;
-  const bool pair_fwd = !no_pairs && mode != XMC_MODE_SIMFP8;
-  const bool pair_upd = !no_pairs;
+  const bool pair_fwd = pairs_ok && mode != XMC_MODE_SIMFP8;
+  const bool pair_upd = pairs_ok;
   if (fwd_fp8) {
     if (int rc = make_map_kmajor(&map_x, true, h->x8, d, xrows, d, pair_fwd ? 128 : 256)) return rc;
   } else {
