@@ -341,7 +341,7 @@ struct DeviceGuard {
 };
 
 // Count a kernel launch; in profile mode also drop an event in front of it.
-enum { K_PREP = 0, K_CONVERT = 1, K_FWD = 2, K_GRADX = 3, K_UPD = 4, K_REDUCE = 5, K_LOGITS = 6, K_END = 7 };
+enum { K_PREP = 0, K_UNUSED = 1, K_FWD = 2, K_GRADX = 3, K_UPD = 4, K_REDUCE = 5, K_LOGITS = 6, K_END = 7 };
 void mark(xmc_handle* h, int kind, cudaStream_t st) {
   if (kind != K_END) ++h->launches;
   if (!h->profile) return;

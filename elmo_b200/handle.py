@@ -128,7 +128,7 @@ class XmcHandle:
     def launch_count(self) -> int:
         return int(self.lib.xmc_launch_count(self._h))
 
-    KINDS = ("prep", "stage_w", "forward", "grad_x", "update", "reduce", "logits", "unused")
+    KINDS = ("prep", "unused1", "forward", "grad_x", "update", "reduce", "logits", "unused7")
 
     def profile(self, enable: bool, read: bool = False):
         """Switch per-kernel-class event timing on/off; with ``read`` return

@@ -174,7 +174,7 @@ int64_t xmc_launch_count(const xmc_handle* h);
  * Per-kernel-class device timing for the bench.  While enabled, every kernel launched by the
  * handle is preceded by a CUDA event on its stream.  A call with non-NULL outputs waits for the
  * recorded events and returns, per class, the summed milliseconds and launch counts since the
- * previous call (8 entries: 0 prep/bucketing, 1 e4m3->bf16 staging, 2 forward, 3 grad_X,
+ * previous call (8 entries: 0 prep/bucketing, 1 unused, 2 forward, 3 grad_X,
  * 4 update, 5 final reductions, 6 logits/top-k), then sets the mode to `enable`.
  */
 int xmc_profile(xmc_handle* h, int32_t enable, double* ms_by_kind, int64_t* launches_by_kind);
