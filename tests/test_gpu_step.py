@@ -59,7 +59,8 @@ def _check_weights(got, want, min_equal=0.999):
 
 @pytest.mark.parametrize("rounding", ["rn", "sr"])
 @pytest.mark.parametrize("L,d,B,nc,sched", [(1024, 128, 48, 2, 256), (1040, 64, 16, 1, 0),
-                                            (4096, 768, 256, 2, 1024), (3000 - 8, 256, 512, 1, 512)])
+                                            (4096, 768, 256, 2, 1024), (3000 - 8, 256, 512, 1, 512),
+                                            (10240, 128, 512, 1, 0)])    # more forward tiles than CTA pairs
 def test_fp8_step_matches_oracle(L, d, B, nc, sched, rounding):
     from oracle import xmc_oracle as O
     w, x, lab = _inputs(L, d, B, 6 * B, seed=L + B)
