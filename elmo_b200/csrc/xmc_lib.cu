@@ -945,6 +945,12 @@ int xmc_forward_logits(xmc_handle* h, const void* x, int32_t x_dtype, int32_t ba
   const int bpad = (int)round_up(batch, 64);
   const bool fwd_fp8 = mode == XMC_MODE_FP8;
   if (int rc = prep_x(h, x, x_dtype, batch, bpad, fwd_fp8, !fwd_fp8, false, st)) return rc;
+  // on CTA pairs (256 batch rows x 256 labels per pair, each CTA staging half of the tile's weight rows)
+  // when the device holds pairs and the weights are multiplied as stored
+  static const bool no_pairs = getenv("XMC_NO_PAIRS") != nullptr;
+  int max_pairs = 0;
+  if (int rc = gradx_configure(h->sm_count, &max_pairs)) return rc;
+  const bool pair = !no_pairs && max_pairs >= 1 && mode != XMC_MODE_SIMFP8;
   CUtensorMap map_x;
   const size_t xrows = (size_t)std::max(h->bpad_max, 256);
   if (fwd_fp8) {
@@ -964,12 +970,13 @@ int xmc_forward_logits(xmc_handle* h, const void* x, int32_t x_dtype, int32_t ba
       if (sim) {
         if (int rc = make_map_raw8(&map_w, wbase, d, rows, d, 256)) return rc;
       } else {
-        if (int rc = make_map_kmajor(&map_w, fwd_fp8, wbase, d, rows, d, 256)) return rc;
+        if (int rc = make_map_kmajor(&map_w, fwd_fp8, wbase, d, rows, d, pair ? 128 : 256)) return rc;
       }
       xmc::LogitsParams lp;
+      lp.m_rows = pair ? 256 : 128;
       lp.batch = batch;
       lp.rows = rows;
-      lp.n_mtiles = cdiv(batch, 128);
+      lp.n_mtiles = cdiv(batch, lp.m_rows);
       lp.n_ntiles = cdiv(rows, 256);
       lp.k_steps = cdiv((long long)d * (fwd_fp8 ? 1 : 2), 128);
       lp.w_scale = h->cfg.w_scale;
@@ -980,9 +987,12 @@ int xmc_forward_logits(xmc_handle* h, const void* x, int32_t x_dtype, int32_t ba
       lp.status = h->status;
       mark(h, K_LOGITS, st);
       const int tiles = lp.n_mtiles * lp.n_ntiles;
-      const int rc = fwd_fp8 ? launch_gemm<xmc::LogitsPolicy<true>>(map_x, map_w, lp, tiles, h->sm_count, st)
-                     : sim   ? launch_gemm<xmc::LogitsPolicy<false, true>>(map_x, map_w, lp, tiles, h->sm_count, st)
-                             : launch_gemm<xmc::LogitsPolicy<false>>(map_x, map_w, lp, tiles, h->sm_count, st);
+      int rc;
+      if (sim) rc = launch_gemm<xmc::LogitsPolicy<false, true>>(map_x, map_w, lp, tiles, h->sm_count, st);
+      else if (pair) rc = fwd_fp8 ? launch_gemm<xmc::LogitsPolicy<true>, true>(map_x, map_w, lp, tiles, h->sm_count, st)
+                                  : launch_gemm<xmc::LogitsPolicy<false>, true>(map_x, map_w, lp, tiles, h->sm_count, st);
+      else rc = fwd_fp8 ? launch_gemm<xmc::LogitsPolicy<true>>(map_x, map_w, lp, tiles, h->sm_count, st)
+                        : launch_gemm<xmc::LogitsPolicy<false>>(map_x, map_w, lp, tiles, h->sm_count, st);
       if (rc) return rc;
     }
     row_base += rows_wc;

@@ -579,8 +579,9 @@ struct UpdPolicy {
 // stores runs of consecutive labels.
 // -------------------------------------------------------------------------------------------------
 struct LogitsParams {
+  int m_rows;              // batch rows per M tile: 128, or 256 on CTA pairs
   int batch, rows;         // valid batch rows, label rows of this launch
-  int n_mtiles, n_ntiles;  // batch tiles of 128, label tiles of 256
+  int n_mtiles, n_ntiles;  // batch tiles of m_rows, label tiles of 256
   int k_steps;
   float w_scale;
   __nv_bfloat16* out;      // [batch x ld_out]
@@ -600,6 +601,7 @@ struct LogitsPolicy {
   static constexpr int kElemsPerRow = FP8 ? 128 : 64;
   static constexpr int kEpiWarps = 8;
   static constexpr int kStages = CONV ? 3 : 4;
+  static constexpr int kStagesPair = 6;
   static constexpr bool kCTile = false;
   static constexpr int kCBufs = 1;
   static constexpr int kConv = CONV ? 2 : 0;      // the weights are the B operand here
@@ -612,7 +614,7 @@ struct LogitsPolicy {
   __device__ static void job(const Params& p, int tile, Job& j) {
     j.t1 = tile / p.n_mtiles;            // label tile (adjacent CTAs share it)
     j.t0 = tile - j.t1 * p.n_mtiles;     // batch tile
-    j.a0 = j.t0 * kTileM;
+    j.a0 = j.t0 * p.m_rows;
     j.b0 = j.t1 * kTileN;
     j.k_begin = 0;
     j.k_steps = p.k_steps;
