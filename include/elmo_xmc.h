@@ -84,6 +84,11 @@ typedef struct {
  * L2 is then reserved for persisting lines process-wide.  xmc_step installs an access-policy window over
  * that private buffer on the caller's stream for the duration of its launches and removes it before it
  * returns; xmc_destroy resets the persisting lines.
+ * The step kernels and the logits kernel are launched as thread-block clusters of two CTAs (CTA pairs,
+ * tcgen05 cta_group::2) with programmatic stream serialization; the library asks the occupancy calculator
+ * how many pairs the device holds and falls back to single-CTA kernels where it holds none.  Switches read
+ * from the environment once per process, for debugging: XMC_NO_PAIRS (single CTAs everywhere), XMC_NO_PDL
+ * (ordinary launches).
  */
 int xmc_create(const xmc_config* cfg, xmc_handle** out);
 int xmc_destroy(xmc_handle* h);
