@@ -247,7 +247,7 @@ __global__ void rescale_e4m3_kernel(uint2* __restrict__ w, long long n8, float f
     uint4 r = make_uint4(0u, 0u, 0u, 0u);
     if (stochastic) {
       const unsigned long long q = (elem0 >> 3) + (unsigned long long)i;
-      r = philox4x32_10(make_uint4((uint32_t)q, (uint32_t)(q >> 32), (uint32_t)step, (uint32_t)(step >> 32)),
+      r = philox4x32_sr(make_uint4((uint32_t)q, (uint32_t)(q >> 32), (uint32_t)step, (uint32_t)(step >> 32)),
                         make_uint2((uint32_t)seed, (uint32_t)(seed >> 32)));
     }
     const uint32_t rr[4] = {r.x, r.y, r.z, r.w};

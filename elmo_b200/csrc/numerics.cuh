@@ -1,5 +1,5 @@
 // Element arithmetic shared by the epilogues: bf16/e4m3 conversions with the reference's
-// intermediate roundings, sigmoid / BCE terms, Philox4x32-10 and rounding of the updated weight.
+// intermediate roundings, sigmoid / BCE terms, the Philox4x32 stream and rounding of the updated weight.
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -41,14 +41,19 @@ __device__ __forceinline__ float bce_softplus(float z) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// Philox4x32-10 (Salmon et al. 2011).  One call serves 8 consecutive weight elements with 16
-// bits each: counter = (q_lo, q_hi, step_lo, step_hi), q = global element index / 8,
-// key = (seed_lo, seed_hi); element j takes half (j & 1) of output word (j >> 1).
+// Philox4x32 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3", SC'11) with kSrRounds = 7
+// rounds: the round function and key schedule of Philox4x32-10, stopped after the seventh round -- the
+// smallest round count its authors report as passing BigCrush (ten is their default margin; the rounds
+// are a quarter of the update epilogue's instructions, and the bits only dither a rounding).  One call
+// serves 8 consecutive weight elements with 16 bits each: counter = (q_lo, q_hi, step_lo, step_hi),
+// q = global element index / 8, key = (seed_lo, seed_hi); element j takes half (j & 1) of output word
+// (j >> 1).
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint2 k) {
+constexpr int kSrRounds = 7;
+__device__ __forceinline__ uint4 philox4x32_sr(uint4 c, uint2 k) {
   constexpr uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
 #pragma unroll
-  for (int r = 0; r < 10; ++r) {
+  for (int r = 0; r < kSrRounds; ++r) {
     const unsigned long long p0 = (unsigned long long)M0 * c.x;
     const unsigned long long p1 = (unsigned long long)M1 * c.z;
     c = make_uint4((uint32_t)(p1 >> 32) ^ c.y ^ k.x, (uint32_t)p1, (uint32_t)(p0 >> 32) ^ c.w ^ k.y, (uint32_t)p0);

@@ -835,7 +835,7 @@ int xmc_step(xmc_handle* h, const void* x, int32_t x_dtype, int32_t batch, const
       up.wd = wd;
       up.seed = seed;
       up.step = step;
-      for (int rd = 0; rd < 10; ++rd) {
+      for (int rd = 0; rd < xmc::kSrRounds; ++rd) {
         up.rkey[rd][0] = (uint32_t)seed + (uint32_t)rd * 0x9E3779B9u;
         up.rkey[rd][1] = (uint32_t)(seed >> 32) + (uint32_t)rd * 0xBB67AE85u;
       }

@@ -256,7 +256,7 @@ struct UpdParams {
   float lr_eff;            // lr / w_scale
   float wd;
   unsigned long long seed, step;
-  uint32_t rkey[10][2];       // Philox round keys (seed + round * Weyl constants), filled on the host: they sit in
+  uint32_t rkey[kSrRounds][2];   // Philox round keys (seed + round * Weyl constants), filled on the host: they sit in
                               // the constant bank, so a round costs two multiplies and two 3-input xors
   unsigned long long elem0;   // global flat element index of W[0][0] of this chunk (Philox counter origin)
   int round_dw_bf16;
@@ -341,7 +341,7 @@ struct UpdPolicy {
     const unsigned long long q = elem >> 3;
     uint4 c = make_uint4((uint32_t)q, (uint32_t)(q >> 32), (uint32_t)p.step, (uint32_t)(p.step >> 32));
 #pragma unroll
-    for (int rd = 0; rd < 10; ++rd) {
+    for (int rd = 0; rd < kSrRounds; ++rd) {
       const unsigned long long p0 = (unsigned long long)M0 * c.x;
       const unsigned long long p1 = (unsigned long long)M1 * c.z;
       c = make_uint4((uint32_t)(p1 >> 32) ^ c.y ^ p.rkey[rd][0], (uint32_t)p1, (uint32_t)(p0 >> 32) ^ c.w ^ p.rkey[rd][1],

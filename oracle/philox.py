@@ -1,8 +1,8 @@
-"""TEST INFRASTRUCTURE ONLY -- CPU restatement of the Philox4x32-10 counter-based RNG.
+"""TEST INFRASTRUCTURE ONLY -- CPU restatement of the Philox4x32 counter-based RNG.
 
 The algorithm is the published one (Salmon et al., "Parallel random numbers: as easy as
-1, 2, 3", SC'11; Random123 library): ten rounds of two 32x32->64 multiplies with the
-constants below and a Weyl key schedule.  The reference obtains its random bits from
+1, 2, 3", SC'11; Random123 library): rounds of two 32x32->64 multiplies with the
+constants below and a Weyl key schedule (ten rounds in Philox4x32-10).  The reference obtains its random bits from
 Triton's ``tl.randint(seed, offset)`` (src/triton_kernels/fuse_kernel.py:30,
 src/triton_kernels/stochastic_rounding_kernel.py:22), which is the same generator with
 counter=(offset,0,0,0) and key=(seed,0), keeping only the first output word.  No
@@ -22,8 +22,12 @@ _MASK = np.uint64(0xFFFFFFFF)
 _SH = np.uint64(32)
 
 
-def philox4x32_10(c0, c1, c2, c3, k0, k1):
-    """Vectorised Philox4x32-10.  All arguments are broadcastable uint32 arrays (or ints).
+SR_ROUNDS = 7      # rounds of the CUDA library's own stochastic-rounding stream (csrc/numerics.cuh: kSrRounds)
+
+
+def philox4x32(c0, c1, c2, c3, k0, k1, rounds=10):
+    """Vectorised Philox4x32 with `rounds` rounds (10 = Philox4x32-10).  All arguments are broadcastable
+    uint32 arrays (or ints).
 
     Returns four uint32 arrays.
     """
@@ -31,7 +35,7 @@ def philox4x32_10(c0, c1, c2, c3, k0, k1):
         *[np.asarray(v, dtype=np.uint64) & _MASK for v in (c0, c1, c2, c3, k0, k1)])
     c0 = c0.copy(); c1 = c1.copy(); c2 = c2.copy(); c3 = c3.copy()
     k0 = k0.copy(); k1 = k1.copy()
-    for _ in range(10):
+    for _ in range(rounds):
         p0 = _M0 * c0                       # 64-bit products; operands < 2^32 so no overflow
         p1 = _M1 * c2
         hi0, lo0 = p0 >> _SH, p0 & _MASK
@@ -45,10 +49,16 @@ def philox4x32_10(c0, c1, c2, c3, k0, k1):
             c2.astype(np.uint32), c3.astype(np.uint32))
 
 
+def philox4x32_10(c0, c1, c2, c3, k0, k1):
+    """Philox4x32-10, the generator Triton's tl.randint is built on."""
+    return philox4x32(c0, c1, c2, c3, k0, k1, 10)
+
+
 def sr_bits16(elem_index, seed, step):
     """16 random bits per weight element, as the CUDA update kernel draws them.
 
-    Keying (defined by this build, not by the reference): one Philox call serves eight
+    Keying (defined by this build, not by the reference): one call of Philox4x32 stopped after
+    SR_ROUNDS = 7 rounds (same round function and key schedule as Philox4x32-10) serves eight
     consecutive elements of a weight row.  counter = (q_lo, q_hi, step_lo, step_hi) with
     q = elem_index // 8, key = (seed_lo, seed_hi).  Element j = elem_index % 8 takes the
     16-bit half (j & 1) of output word (j >> 1).  ``elem_index`` is the GLOBAL flat index
@@ -59,7 +69,7 @@ def sr_bits16(elem_index, seed, step):
     q = e >> np.uint64(3)
     j = (e & np.uint64(7)).astype(np.int64)
     seed = np.uint64(seed); step = np.uint64(step)
-    x = philox4x32_10(q & _MASK, q >> _SH, step & _MASK, step >> _SH, seed & _MASK, seed >> _SH)
+    x = philox4x32(q & _MASK, q >> _SH, step & _MASK, step >> _SH, seed & _MASK, seed >> _SH, SR_ROUNDS)
     words = np.stack(x, axis=0)                                  # [4, ...]
     w = np.take_along_axis(words, (j >> 1)[None, ...], axis=0)[0]
     return ((w >> ((j & 1) * 16).astype(np.uint32)) & np.uint32(0xFFFF)).astype(np.uint32)

@@ -3,15 +3,16 @@
  * CPU baseline is not dominated by numpy's Philox.  tests/test_oracle_philox.py checks that
  * this file and the numpy statements agree bit for bit.
  *
- * Philox4x32-10: Salmon et al., "Parallel random numbers: as easy as 1, 2, 3" (SC'11).
+ * Philox4x32: Salmon et al., "Parallel random numbers: as easy as 1, 2, 3" (SC'11).
  * Build: gcc -O3 -fopenmp -shared -fPIC -o oracle/_build/liboracle_sr.so oracle/sr_philox.c
  */
 #include <math.h>
 #include <stdint.h>
 #include <string.h>
 
-static inline void philox4x32_10(uint32_t c[4], uint32_t k0, uint32_t k1) {
-  for (int r = 0; r < 10; ++r) {
+#define SR_ROUNDS 7   /* as oracle/philox.py: the library's stream stops Philox4x32 after seven rounds */
+static inline void philox4x32_sr(uint32_t c[4], uint32_t k0, uint32_t k1) {
+  for (int r = 0; r < SR_ROUNDS; ++r) {
     const uint64_t p0 = (uint64_t)0xD2511F53u * c[0];
     const uint64_t p1 = (uint64_t)0xCD9E8D57u * c[2];
     const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c[1] ^ k0;
@@ -28,7 +29,7 @@ static inline void philox4x32_10(uint32_t c[4], uint32_t k0, uint32_t k1) {
 static inline uint32_t bits16(uint64_t elem, uint64_t seed, uint64_t step) {
   const uint64_t q = elem >> 3;
   uint32_t c[4] = {(uint32_t)q, (uint32_t)(q >> 32), (uint32_t)step, (uint32_t)(step >> 32)};
-  philox4x32_10(c, (uint32_t)seed, (uint32_t)(seed >> 32));
+  philox4x32_sr(c, (uint32_t)seed, (uint32_t)(seed >> 32));
   const int j = (int)(elem & 7);
   return (c[j >> 1] >> (16 * (j & 1))) & 0xFFFFu;
 }

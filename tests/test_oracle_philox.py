@@ -1,4 +1,5 @@
-"""Philox4x32-10 known answers and the stochastic-rounding definitions of the oracle."""
+"""Philox4x32 known answers (ten rounds), the seven-round stream of the library, and the stochastic-rounding
+definitions of the oracle."""
 import numpy as np
 import torch
 
@@ -19,10 +20,25 @@ def test_philox_known_answers():
         assert got == want
 
 
+def test_seven_rounds_are_a_prefix_of_the_ten_pinned_above():
+    """The library's stream stops the same round function after seven rounds: three more rounds with the
+    key schedule advanced by seven steps must give the ten-round output that the known answers pin."""
+    rng = np.random.default_rng(7)
+    c = [rng.integers(0, 1 << 32, size=64, dtype=np.uint64) for _ in range(4)]
+    k = [rng.integers(0, 1 << 32, size=64, dtype=np.uint64) for _ in range(2)]
+    seven = philox.philox4x32(*c, *k, 7)
+    k7 = [(k[0] + 7 * 0x9E3779B9) & 0xFFFFFFFF, (k[1] + 7 * 0xBB67AE85) & 0xFFFFFFFF]
+    ten = philox.philox4x32(*[v.astype(np.uint64) for v in seven], *k7, 3)
+    want = philox.philox4x32_10(*c, *k)
+    assert philox.SR_ROUNDS == 7
+    for a, b in zip(ten, want):
+        assert np.array_equal(a, b)
+
+
 def test_sr_bits_layout():
     idx = np.arange(64, dtype=np.uint64) + 8 * 12345
     r = philox.sr_bits16(idx, seed=0x1234567812345678, step=3)
-    x = philox.philox4x32_10(12345, 0, 3, 0, 0x12345678, 0x12345678)
+    x = philox.philox4x32(12345, 0, 3, 0, 0x12345678, 0x12345678, philox.SR_ROUNDS)
     assert int(r[0]) == int(x[0]) & 0xFFFF and int(r[1]) == int(x[0]) >> 16
     assert int(r[7]) == int(x[3]) >> 16
     assert r.max() < 65536 and len(np.unique(r)) > 56
