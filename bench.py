@@ -40,7 +40,7 @@ METRIC = "xmc_layer_train_samples_per_sec"
 UNIT = "samples/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch over 65 536 label rows (batch 512, d 768, e4m3
 # weights), per label row, from an ncu capture of each kernel of the step
-DRAM_BYTES_PER_ROW = {"update": 136.1e6 / 65536, "grad_x": 121.5e6 / 65536, "forward": 69.2e6 / 65536}
+DRAM_BYTES_PER_ROW = {"update": 137.1e6 / 65536, "grad_x": 121.6e6 / 65536, "forward": 68.2e6 / 65536}
 
 
 # --------------------------------------------------------------------------------------------
